@@ -70,6 +70,10 @@ class ModelSpec:
     head: PartSpec                  # family "head", e.g. kind "linear" with tied=True/False
     max_position: int
     stop_token_ids: Tuple[int, ...] = ()
+    # copies of the residual stream that the blocks keep per token (1: the one stream).  With more, the stream tensor
+    # is float32 [streams, T, hidden]: the embedding fills the first copy, the decoder repeats it into the others, and
+    # the rows that reach the final norm are the sum of the copies; every block must be of a kind that takes them.
+    streams: int = 1
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -3,7 +3,9 @@
 // mask (a token sees only keys of its own chunk of `chunk` positions, counted from position 0),
 // optional per-head sink (one more term exp(sink[h]) in the softmax denominator, with no key and
 // no value), values of their own size `hdv` <= head size, optionally only the tokens that
-// `token_list` names (T of them).
+// `token_list` names (T of them).  Optional per head: a factor on the scaled score (`head_scale`), a distance bias
+// (`slopes`: slope[h] * (query position - key position) is taken off the score) and an output gate (`gate` float32
+// [T, ldg]: the head's output is multiplied by sigmoid(gate[t][h])).
 //
 // It serves the true-32-bit engine for every kind of step (whole prompts, portions with an
 // offset, single decoded tokens) and is the plain kernel the faster attention kernels are
@@ -28,7 +30,9 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                TO* __restrict__ out, long out_stride,
                                int nq, int nkv, int hd, int page_size, int window, float scale,
-                               int chunk, const float* __restrict__ sinks, int hdv, const int* __restrict__ token_list) {
+                               int chunk, const float* __restrict__ sinks, int hdv, const int* __restrict__ token_list,
+                               const float* __restrict__ head_scale, const float* __restrict__ slopes,
+                               const float* __restrict__ gate, long ldg) {
     __shared__ float qs[256];
     __shared__ float p[AG_THREADS];
     __shared__ int slots[AG_THREADS];
@@ -42,6 +46,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
 
     for (int d = tid; d < hd; d += AG_THREADS) qs[d] = to_f(q[(size_t)t * q_stride + (size_t)h * hd + d]);
     __syncthreads();
+    const float hscale = head_scale ? head_scale[h] : 1.0f;
+    const float slope = slopes ? slopes[h] : 0.0f;
 
     float m = -INFINITY, l = 0.f;
     float acc0 = 0.f, acc1 = 0.f;                      // dims tid and tid + 128
@@ -57,6 +63,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                 float dot = 0.f;
                 for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f(kp[d]), dot);
                 score = dot * scale;
+                if (head_scale) score *= hscale;
+                if (slopes) score -= slope * (float)(pos - j);
             }
         }
         slots[tid] = slot;
@@ -90,7 +98,8 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
         acc0 *= corr;
         acc1 *= corr;
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;        // empty context gives zeros (backend.rs:320)
+    float inv = l > 0.f ? 1.0f / l : 0.f;              // empty context gives zeros (backend.rs:320)
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
     TO* o = out + (size_t)t * out_stride + (size_t)h * hdv;
     if (tid < hdv) o[tid] = from_f<TO>(acc0 * inv);
     if (tid + AG_THREADS < hdv) o[tid + AG_THREADS] = from_f<TO>(acc1 * inv);
@@ -104,7 +113,8 @@ AIEN_API int aien_paged_attention_generic(
     const void* q, long q_stride, const void* k_cache, const void* v_cache,
     const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
     void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale,
-    int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, const int* token_list, cudaStream_t stream) {
+    int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, const int* token_list,
+    const float* head_scale, const float* slopes, const float* gate, long ldg, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hdv <= 0) hdv = hd;
     if (hd <= 0 || hd > 256 || hdv > 256 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || chunk < 0) return AIEN_E_SHAPE;
@@ -113,6 +123,7 @@ AIEN_API int aien_paged_attention_generic(
     AIEN_DISPATCH_DTYPE(act_dt, TQ, AIEN_DISPATCH_DTYPE(kv_dt, TKV,
         (paged_attention_generic_kernel<TQ, TKV, TQ><<<grid, AG_THREADS, 0, stream>>>(
             (const TQ*)q, q_stride, (const TKV*)k_cache, (const TKV*)v_cache, block_table, max_blocks,
-            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv, token_list))));
+            seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv, token_list,
+            head_scale, slopes, gate, ldg))));
     return launch_status();
 }

@@ -21,7 +21,9 @@
 
 namespace aien {
 
+// kind 0: gelu (erf form), 1: gelu (tanh form), 2: the square of relu
 __device__ __forceinline__ float act_apply(float z, int kind) {
+    if (kind == 2) { const float r = fmaxf(z, 0.f); return r * r; }
     if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
 }

@@ -117,7 +117,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
         "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
-        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P, P],
+        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P, P, P, P, L, P],
         "aien_branch_norm_add": [P, P, I, I, c_size_t, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
         "aien_stream_norm_inplace": [P, P, I, F, P, I, I, I, P],
         "aien_qk_rope_pairs_unit_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, I, I, F, P, P, I, P, P, P, I, I, I, P],
@@ -173,6 +173,15 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_embed_gather_scaled": [P, I, P, P, I, I, I, F, P],
         "aien_gelu_times_table": [P, I, L, P, I, L, I, P, I, P, I, L, I, I, P],
         "aien_softcap": [P, c_size_t, F, P],
+        "aien_replicate_streams": [P, c_size_t, I, P],
+        "aien_hc_norm": [P, I, P, I, I, c_size_t, P, P, P, I, F, P, I, I, I, P, I, P, P, P, P],
+        "aien_token_shift": [P, P, I, P, P, P, P, P, P, I, I, I, P],
+        "aien_hc_sum_rows": [P, I, I, P, I, I, c_size_t, P, P, P, I, I, P],
+        "aien_embed_gather_sinusoid": [P, I, P, P, P, P, I, I, I, F, P],
+        "aien_attn_conv_prepare": [P, L, I, I, I, I, I, I, P, P, P, I, I, P, P, I, F, I, I, I, P, P, P, P, P, P, P, P, I, P, I, L, I, P],
+        "aien_delta_conv_prepare": [P, L, I, I, I, I, I, I, I, I, I, P, P, P, I, I, P, P, I, P, c_size_t, P, P, P, P, P, L, P, L, I, P],
+        "aien_delta_rule": [P, L, I, I, I, P, L, P, c_size_t, c_size_t, P, P, P, P, L, I, I, I, I, I, P],
+        "aien_grouped_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, I, I, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
     }
@@ -446,7 +455,8 @@ def qk_rope_pairs_unit_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: O
 
 
 # ---------------------------------------------------------------------------- routed feed-forward
-ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1}
+ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "relu2": 2}      # relu2: the square of relu
+ACT_IN_PRODUCT = (0, 1)             # the kinds that the products' epilogues know; the others run as a kernel behind the product
 
 
 def moe_route(z: torch.Tensor, groups: int, keep: int, top: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor,
@@ -592,14 +602,21 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             max_blocks: int, seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                             num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                             scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None, value_dim: int = 0,
-                            token_list: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None) -> None:
+                            token_list: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None,
+                            head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                            gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention of T query tokens over their requests' pages.  q [T, nq*hd] (row stride
     free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd].
     ``chunk`` > 0: a token sees only the keys of its own chunk of that many positions.  ``sinks``
     (float32 [nq]): one more term exp(sink) in every head's softmax denominator.  ``value_dim``:
     size of a value when it differs from the head size (v_cache [slots, nkv, value_dim], out [T, nq*value_dim]).
-    ``token_list`` (int32) with ``num_tokens``: only these tokens of the step are served."""
-    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks, token_list)
+    ``token_list`` (int32) with ``num_tokens``: only these tokens of the step are served.  Per head (float32 [nq]):
+    ``head_scale`` multiplies the scaled score, ``slopes`` takes slope * (query position - key position) off it;
+    ``gate`` (float32 [T, >= nq], row stride free): the head's output is multiplied by sigmoid(gate[t, h])."""
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks, token_list, head_scale, slopes, gate)
+    for v in (head_scale, slopes):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == num_q_heads)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] >= num_q_heads)
     if sinks is not None:
         assert sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads
     T = q.shape[0] if token_list is None else int(num_tokens)
@@ -610,7 +627,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     _check(lib().aien_paged_attention_generic(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window, float(scale),
-        dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _p(token_list), _stream()), "paged_attention_generic")
+        dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _p(token_list), _p(head_scale), _p(slopes), _p(gate),
+        gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_generic")
 
 
 # ---------------------------------------------------------------------------- sampling
@@ -1437,3 +1455,179 @@ def latent_attention_tc_ksplit(num_tokens: int, num_seqs: int, heads: int, max_c
     span = min(window, max_ctx) if window > 0 else max_ctx
     blocks = max(1, (span + LATENT_TC_TILE - 1) // LATENT_TC_TILE + 1)
     return max(1, min(blocks, 296 // tiles)) if tiles <= 148 else 1
+
+
+# ---------------------------------------------------------------------------- several residual streams, token shift
+def replicate_streams(x: torch.Tensor) -> None:
+    """x float32 [n, T, H]: copies x[0] into x[1:]."""
+    _dev(x)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 3
+    _check(lib().aien_replicate_streams(_p(x), x.shape[1] * x.shape[2], x.shape[0], _stream()), "replicate_streams")
+
+
+def _pending(y: Optional[torch.Tensor], T: int, H: int) -> tuple:
+    if y is None:
+        return 0, F32, 1, 0
+    assert y.is_contiguous()
+    if y.dim() == 3:
+        assert y.dtype == torch.float32 and tuple(y.shape[1:]) == (T, H)
+        return _p(y), F32, y.shape[0], T * H
+    assert tuple(y.shape) == (T, H)
+    return _p(y), dt(y), 1, 0
+
+
+def hc_norm(x: torch.Tensor, y: Optional[torch.Tensor], prev: Optional[torch.Tensor], cur: torch.Tensor, weight: torch.Tensor,
+            eps: float, h: torch.Tensor, shift_w: Optional[torch.Tensor] = None, shift_state: Optional[torch.Tensor] = None,
+            slot_map: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+    """Streams x float32 [n, T, H] with sublayer packs [in(n) | out(n) | mix(n*n)] (float32; mix indexed [from, to]):
+    first, when ``y`` is given (a branch output [T, H], or float32 partial products [P, T, H]), the write that ``prev``
+    describes, in place: x_t <- sum_s mix[s, t] x_s + out[t] y; then u = sum_s in[s] x_s with ``cur``'s in, and
+    h = u / sqrt(mean u^2 + eps) * weight.  With ``shift_w`` (a step of single tokens): h <- h + (h' - h) * shift_w,
+    h' the row that request's slot ``shift_state[slot_map[t]]`` held (zeros at position 0); the slot then holds h
+    as it was before the shift."""
+    _dev(x, y, prev, cur, weight, h, shift_w, shift_state, slot_map, positions)
+    n, T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and h.is_contiguous() and tuple(h.shape) == (T, H)
+    assert cur.dtype == torch.float32 and cur.numel() == 2 * n + n * n and (prev is None or (prev.dtype == torch.float32 and prev.numel() == cur.numel()))
+    assert weight.numel() == H and weight.is_contiguous()
+    if shift_w is not None:
+        assert shift_w.numel() == H and shift_state.dtype == torch.float32 and shift_state.is_contiguous() and shift_state.shape[-1] == H
+        assert slot_map.dtype == torch.int32 and positions.dtype == torch.int32
+    yp, ydt, parts, stride = _pending(y, T, H)
+    _check(lib().aien_hc_norm(_p(x), n, yp, ydt, parts, stride, _p(prev), _p(cur), _p(weight), dt(weight), float(eps), _p(h), dt(h), T, H,
+                              _p(shift_w), dt(shift_w) if shift_w is not None else F32, _p(shift_state), _p(slot_map), _p(positions),
+                              _stream()), "hc_norm")
+
+
+def token_shift(hn: torch.Tensor, shift_w: torch.Tensor, state: torch.Tensor, slot_map: torch.Tensor, seq_of_token: torch.Tensor,
+                q_start: torch.Tensor, positions: torch.Tensor, h: torch.Tensor) -> None:
+    """h[t] = hn[t] + (hn[t-1] - hn[t]) * shift_w within a request; the row before a portion's first token comes from
+    the request's slot of ``state`` (float32 [slots, H]; zeros at position 0), which then takes the portion's last row."""
+    _dev(hn, shift_w, state, slot_map, seq_of_token, q_start, positions, h)
+    T, H = hn.shape
+    assert hn.dtype == torch.float32 and hn.is_contiguous() and h.is_contiguous() and tuple(h.shape) == (T, H)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[-1] == H and shift_w.numel() == H
+    _check(lib().aien_token_shift(_p(hn), _p(shift_w), dt(shift_w), _p(state), _p(slot_map), _p(seq_of_token), _p(q_start), _p(positions),
+                                  _p(h), dt(h), T, H, _stream()), "token_shift")
+
+
+def hc_sum_rows(x: torch.Tensor, y: Optional[torch.Tensor], prev: Optional[torch.Tensor], rows: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = sum over the streams of x[:, rows[r]], after the pending write (``y`` with the pack ``prev``) if given."""
+    _dev(x, y, prev, rows, out)
+    n, T, H = x.shape
+    R = out.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == H
+    assert rows.dtype == torch.int32 and rows.numel() >= R
+    yp, ydt, parts, stride = _pending(y, T, H)
+    _check(lib().aien_hc_sum_rows(_p(x), n, T, yp, ydt, parts, stride, _p(prev), _p(rows), _p(out), R, H, _stream()), "hc_sum_rows")
+
+
+def embed_gather_sinusoid(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, x: torch.Tensor,
+                          scale: float) -> None:
+    """x[t] = table[ids[t]] * scale + s(positions[t]); s(p)[2i] = sin(p f_i), s(p)[2i+1] = cos(p f_i), f = inv_freq (float64)."""
+    _dev(table, ids, positions, inv_freq, x)
+    T, H = x.shape
+    assert table.is_contiguous() and x.is_contiguous() and x.dtype == torch.float32 and table.shape[1] == H
+    assert ids.dtype == torch.int32 and positions.dtype == torch.int32 and inv_freq.dtype == torch.float64 and inv_freq.numel() >= (H + 1) // 2
+    _check(lib().aien_embed_gather_sinusoid(_p(table), dt(table), _p(ids), _p(positions), _p(inv_freq), _p(x), T, H, table.shape[0],
+                                            float(scale), _stream()), "embed_gather_sinusoid")
+
+
+# ---------------------------------------------------------------------------- short convolutions, the delta rule
+def attn_conv_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, Cq: int, Ck: int, Cv: int, wq: torch.Tensor,
+                      wk: Optional[torch.Tensor], wv: Optional[torch.Tensor], taps: int, q_norm: torch.Tensor, k_norm: Optional[torch.Tensor],
+                      eps: float, kv_heads: int, value_dim: int, value_norm: bool, state: Optional[torch.Tensor], state_slots: torch.Tensor,
+                      seq_of_token: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, kv_slots: Optional[torch.Tensor],
+                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], q_out: torch.Tensor) -> None:
+    """Causal convolution over time (``taps`` taps, weights [C, taps]) of the q block (and, with Ck > 0, the k and v
+    blocks) of ``proj`` float32 [T, *]; RMS norm of the whole q row and of the whole k row with the plain weights
+    ``q_norm`` / ``k_norm``; with ``value_norm`` every value head divided by its root mean square.  q goes to ``q_out``
+    [T, Cq]; k and v to the token's slot ``kv_slots[t]`` of the caches.  ``state`` float32 [slots, (taps-1) * (Cq+Ck+Cv)]
+    keeps every request's last taps-1 projected rows between steps."""
+    _dev(proj, wq, wk, wv, q_norm, k_norm, state, state_slots, seq_of_token, q_start, positions, kv_slots, k_cache, v_cache, q_out)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.shape == (T, Cq)
+    ws = [w for w in (wq, wk, wv) if w is not None]
+    assert all(w.is_contiguous() and w.dtype == wq.dtype and w.shape[1] == taps for w in ws)
+    assert q_norm.is_contiguous() and q_norm.numel() == Cq and (k_norm is None or (k_norm.dtype == q_norm.dtype and k_norm.numel() == Ck))
+    if taps > 1:
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == (taps - 1) * (Cq + Ck + Cv)
+    if Ck > 0:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype and kv_slots.dtype == torch.int32
+    _check(lib().aien_attn_conv_prepare(
+        _p(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), int(Cq), int(Ck), int(Cv), _p(wq), _p(wk), _p(wv), dt(wq), int(taps),
+        _p(q_norm), _p(k_norm), dt(q_norm), float(eps), int(kv_heads), int(value_dim), 1 if value_norm else 0, _p(state), _p(state_slots),
+        _p(seq_of_token), _p(q_start), _p(positions), _p(kv_slots), _p(k_cache), _p(v_cache), dt(k_cache) if k_cache is not None else dt(q_out),
+        _p(q_out), dt(q_out), q_out.stride(0), T, _stream()), "attn_conv_prepare")
+
+
+def delta_conv_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, b_off: int, a_off: int, qk_heads: int, dim: int, heads: int,
+                       vdim: int, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, taps: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                       state: torch.Tensor, state_slots: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
+                       positions: torch.Tensor, out: torch.Tensor, gb: torch.Tensor) -> None:
+    """The inputs of the gated delta rule from ``proj`` float32 [T, *]: convolution over time and silu of q, k (qk_heads x
+    dim each) and v (heads x vdim); q and k made unit vectors per head, q times dim^-1/2 -> ``out`` float32 [T, q | k | v];
+    per head the decay exp(-exp(a_log) * softplus(a + dt_bias)) and beta = sigmoid(b) -> ``gb`` float32 [T, 2 * heads].
+    ``state`` float32 [slots, n]: the first (taps-1) * channels numbers of a slot are the convolution's."""
+    _dev(proj, wq, wk, wv, a_log, dt_bias, state, state_slots, seq_of_token, q_start, positions, out, gb)
+    T = proj.shape[0]
+    C = 2 * qk_heads * dim + heads * vdim
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.float32 and out.shape == (T, C) and out.stride(1) == 1
+    assert gb.dtype == torch.float32 and gb.shape == (T, 2 * heads) and gb.stride(1) == 1
+    assert all(w.is_contiguous() and w.dtype == wq.dtype and w.shape[1] == taps for w in (wq, wk, wv))
+    assert a_log.dtype == dt_bias.dtype and a_log.numel() == heads and dt_bias.numel() == heads and a_log.is_contiguous() and dt_bias.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] >= (taps - 1) * C
+    _check(lib().aien_delta_conv_prepare(
+        _p(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), int(b_off), int(a_off), int(qk_heads), int(dim), int(heads), int(vdim),
+        _p(wq), _p(wk), _p(wv), dt(wq), int(taps), _p(a_log), _p(dt_bias), dt(a_log), _p(state), state.shape[1], _p(state_slots),
+        _p(seq_of_token), _p(q_start), _p(positions), _p(out), out.stride(0), _p(gb), gb.stride(0), T, _stream()), "delta_conv_prepare")
+
+
+def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, gb: torch.Tensor, state: torch.Tensor, s_off: int,
+               slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, o: torch.Tensor, num_seqs: int, heads: int,
+               qk_heads: int, dim: int, vdim: int) -> None:
+    """Per value head, token by token: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, all float32.  ``qkv``
+    float32 [T, *] holds the prepared q, k (qk_heads x dim) and v (heads x vdim), ``gb`` [T, 2 * heads] the decay g and
+    beta.  S [heads, dim, vdim] of request s lies ``s_off`` numbers into slot slot_map[s] of ``state`` (float32 [slots, n])."""
+    _dev(qkv, gb, state, slot_map, q_start, positions, o)
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and gb.dtype == torch.float32 and gb.stride(1) == 1
+    assert o.dtype == torch.float32 and o.stride(1) == 1 and o.shape[1] == heads * vdim
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2 and state.shape[1] >= s_off + heads * dim * vdim
+    _check(lib().aien_delta_rule(_p(qkv), qkv.stride(0), int(q_off), int(k_off), int(v_off), _p(gb), gb.stride(0), _p(state), state.shape[1],
+                                 int(s_off), _p(slot_map), _p(q_start), _p(positions), _p(o), o.stride(0), int(num_seqs), int(heads),
+                                 int(qk_heads), int(dim), int(vdim), _stream()), "delta_rule")
+
+
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
+
+
+def grouped_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, group: int,
+                          gate_act: str = "sigmoid") -> None:
+    """out = o / sqrt(mean over each group of ``group`` neighbouring columns of o^2 + eps) * weight[column mod group] *
+    act(gate); o float32 [T, N], gate [T, N] (row stride free), weight [group] shared by the groups."""
+    _dev(o, gate, weight, out)
+    T, N = o.shape
+    assert o.dtype == torch.float32 and o.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1 and N % group == 0
+    assert tuple(gate.shape) == (T, N) and tuple(out.shape) == (T, N) and weight.numel() == group and weight.is_contiguous()
+    _check(lib().aien_grouped_gated_rmsnorm(_p(o), o.stride(0), _p(gate), dt(gate), gate.stride(0), _p(weight), dt(weight), float(eps),
+                                            _p(out), dt(out), out.stride(0), T, N // group, int(group), GATE_ACTS[gate_act], _stream()),
+           "grouped_gated_rmsnorm")
+
+
+# ---------------------------------------------------------------------------- attention with a distance bias
+def biased_attention_workspace_bytes(lim, num_heads: int, value_dim: int, window: int) -> int:
+    """Scratch of :func:`biased_attention` for the largest step."""
+    return 4096
+
+
+def biased_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor, num_q_heads: int,
+                     num_kv_heads: int, head_dim: int, value_dim: int, window: int, scale: float, head_scale: Optional[torch.Tensor],
+                     slopes: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> None:
+    """Attention of the step's tokens over one cache group with, per head, a factor on the scaled score, a bias
+    -slope * (query position - key position) and a sigmoid gate on the output; an optional window; values of size
+    ``value_dim``.  Picks the kernel for the step."""
+    k2 = k_cache.view(-1, num_kv_heads, head_dim)
+    v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim,
+                            head_scale=head_scale, slopes=slopes, gate=gate)

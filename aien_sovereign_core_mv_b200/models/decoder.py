@@ -69,6 +69,28 @@ class Decoder:
                 if self.group_needs[g].group_key() != need.group_key():
                     raise ValueError(f"a run reads cache slot {run.cache} whose layout differs from its own")
                 self.bindings.append(RunBinding(g, s, False))
+        # ---- states that parts keep beside the mixer's cache: one per run and part, grouped by shape
+        for run, binding in zip(spec.run_list, self.bindings):
+            block = self.blocks[run.layer]
+            for part in [block] + list(block.parts().values()):
+                need = part.state_need()
+                if need is None:
+                    continue
+                if need.kind != "state":
+                    raise ValueError("state_need() must return a CacheNeed of kind 'state'")
+                key = need.group_key()
+                for g, have in enumerate(self.group_needs):
+                    if have.group_key() == key:
+                        break
+                else:
+                    g = len(self.group_needs)
+                    self.group_needs.append(need)
+                    self.group_slots.append(0)
+                binding.states[id(part)] = (g, self.group_slots[g])
+                self.group_slots[g] += 1
+        self.streams = int(spec.streams)
+        if self.streams > 1 and not all(getattr(b, "takes_streams", False) for b in self.blocks):
+            raise ValueError("a model with several residual streams needs blocks that take them (takes_streams)")
 
     # ------------------------------------------------------------------ construction
     def _position(self, ps: PartSpec):
@@ -172,7 +194,7 @@ class Decoder:
         return max(max(b.workspace_bytes(lim) for b in self.blocks), head) + (1 << 16)
 
     def step_workspace_bytes(self, lim) -> int:
-        n = lim.max_tokens * self.hidden_size * 4 + 4096
+        n = self.streams * lim.max_tokens * self.hidden_size * 4 + 4096
         for p in self._positions.values():
             if hasattr(p, "step_workspace_bytes"):
                 n += p.step_workspace_bytes(lim.max_tokens)
@@ -183,8 +205,13 @@ class Decoder:
         """Runs the step's tokens through the run list; writes float32 logits of the wanted
         rows into ``logits`` [num_rows, vocab]."""
         ws = ctx.workspace
-        x = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
-        self.embedding.forward(ctx, ctx.token_ids, x)
+        if self.streams > 1:
+            x = ws.take_step((self.streams, ctx.num_tokens, self.hidden_size), torch.float32)
+            self.embedding.forward(ctx, ctx.token_ids, x[0])
+            K.replicate_streams(x)
+        else:
+            x = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
+            self.embedding.forward(ctx, ctx.token_ids, x)
         delta = None
         runs = self.spec.run_list
         for i, (run, binding) in enumerate(zip(runs, self.bindings)):
@@ -201,7 +228,12 @@ class Decoder:
             delta = None
         if num_rows > 0:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)
-            K.gather_add_rows(x, delta, want_rows, rows)
+            if hasattr(delta, "sum_rows"):                      # a block that keeps several streams sums them itself
+                delta.sum_rows(ctx, x, want_rows, rows)
+            elif self.streams > 1:
+                K.hc_sum_rows(x, None, None, want_rows, rows)
+            else:
+                K.gather_add_rows(x, delta, want_rows, rows)
             hn = self.final_norm.forward(ctx, rows, None)
             self.head.forward(ctx, hn, logits)
         return logits

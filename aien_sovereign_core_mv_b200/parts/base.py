@@ -88,11 +88,22 @@ class GroupView:
 
 @dataclass
 class RunBinding:
-    """Where one run of a layer keeps its cache."""
+    """Where one run of a layer keeps its cache, and where the parts of the run keep a state of their own."""
 
     group: int = -1          # cache group index, -1: none
     slot: int = -1           # index of this run's planes inside the group's storage
     writes: bool = True      # False: attend over planes another run wrote
+    # id(part) -> (state group, index of this run inside it), for every part of the run's block that declares a
+    # ``state_need()`` (a fixed-size state per request beside the mixer's cache)
+    states: Dict[int, Tuple[int, int]] = field(default_factory=dict)
+
+    def state_of(self, ctx: "StepContext", part: "Part") -> Tuple[torch.Tensor, torch.Tensor]:
+        """(state [slots + 1, *shape], slot_map [S]) of ``part`` in this run: request s of the step owns slot
+        ``slot_map[s]``; the rules of :class:`GroupView` hold (a portion whose first token has position 0 starts
+        from nothing; the last slot is nobody's)."""
+        g, i = self.states[id(part)]
+        view = ctx.groups[g]
+        return view.storage["state"][i], view.slot_map
 
 
 @dataclass
@@ -255,6 +266,12 @@ class Part:
     def workspace_bytes(self, lim: "StepLimits") -> int:
         """Upper bound of what forward() takes from the layer workspace within `lim`."""
         return 0
+
+    def state_need(self) -> Optional[CacheNeed]:
+        """A state of fixed size per request that this part (a block, a mixer, ...) keeps between steps *beside* the
+        mixer's cache: a ``CacheNeed`` of kind "state", or None.  Every run of the layer gets its own; forward()
+        finds it with ``run.state_of(ctx, self)``."""
+        return None
 
 
 class Norm(Part):

@@ -19,13 +19,16 @@ class TableEmbedding(Embedding):
 
     ``scale``: the row is multiplied by this constant.  ``side_width`` > 0: the part also owns a second table
     ``side`` [vocab, side_width] that it does not read itself; layers with a per-token side input take their columns
-    of it (``side_table``)."""
+    of it (``side_table``).  ``sinusoid_base`` b > 0: the sinusoidal vector of the token's position is added, entry
+    2i = sin(p * b^(-2i/hidden)), entry 2i+1 = cos of the same angle (the angle in float64, as the rotary tables)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, side_width: int = 0):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, side_width: int = 0, sinusoid_base: float = 0.0):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.scale, self.side_width = float(scale), int(side_width)
+        self.sinusoid_base = float(sinusoid_base or 0.0)
         self.weight: Optional[torch.Tensor] = None
         self.side: Optional[torch.Tensor] = None
+        self.inv_freq: Optional[torch.Tensor] = None
 
     def param_shapes(self):
         shapes = {"weight": ((self.vocab_size, self.hidden_size), "embedding")}
@@ -37,6 +40,10 @@ class TableEmbedding(Embedding):
         self.weight = tensors["weight"].contiguous()
         if self.side_width > 0:
             self.side = tensors["side"].contiguous()
+        if self.sinusoid_base > 0.0:
+            H = self.hidden_size
+            f = [self.sinusoid_base ** (-2.0 * i / H) for i in range((H + 1) // 2)]
+            self.inv_freq = torch.tensor(f, dtype=torch.float64, device=self.weight.device)
 
     def tied_weight(self):
         return self.weight
@@ -51,7 +58,10 @@ class TableEmbedding(Embedding):
             K.embed_gather(self.weight, token_ids, x)
 
     def forward(self, ctx: StepContext, token_ids: torch.Tensor, x: torch.Tensor) -> None:
-        self._gather(token_ids, x)
+        if self.inv_freq is not None:
+            K.embed_gather_sinusoid(self.weight, token_ids, ctx.positions, self.inv_freq, x, self.scale)
+        else:
+            self._gather(token_ids, x)
 
 
 @register_embedding("table_normed")
@@ -62,7 +72,7 @@ class NormedTableEmbedding(TableEmbedding):
     by the table itself."""
 
     def __init__(self, vocab_size: int, hidden_size: int, norm: dict, scale: float = 1.0, side_width: int = 0):
-        super().__init__(vocab_size, hidden_size, scale, side_width)
+        super().__init__(vocab_size, hidden_size, scale, side_width, 0.0)
         params = {k: v for k, v in dict(norm).items() if k != "kind"}
         self.norm = make_part("norm", norm["kind"], size=self.hidden_size, **params)
         if not hasattr(self.norm, "norm_stream"):

@@ -22,7 +22,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
            out: Optional[torch.Tensor] = None, may_defer_sum: bool = False, act: Optional[int] = None) -> torch.Tensor:
     """a [M, K] (row stride free), w [N, K] -> [M, N] taken from the step workspace.
 
-    ``act`` (0: the gelu in its erf form, 1: in its tanh form): the activation of every value of the
+    ``act`` (``kernels.ACT_KINDS``; 0: the gelu in its erf form, 1: in its tanh form, 2: the square of relu): the activation of every value of the
     product, in the product's epilogue where the kernel has one (bfloat16 results of the streamed
     decode product and of the tensor-core kernel), else by a kernel of its own behind it.
 
@@ -49,7 +49,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: Option
     if out is None:
         out = ctx.workspace.take((M, N), out_dtype or a.dtype)
     choice = _FORCE or _choose(a, w, out, M)
-    fused = act is not None and out.dtype == torch.bfloat16 and out.is_contiguous()
+    fused = act is not None and act in K.ACT_IN_PRODUCT and out.dtype == torch.bfloat16 and out.is_contiguous()
     if choice == "gemv":
         fused = fused and K.gemv_takes_activation(a.shape[1])
         K.gemv(a, w, out, epilogue=3 + act if fused else 0)

@@ -66,8 +66,8 @@ class SwiGLU(FeedForward):
 
 @register_feed_forward("mlp_act")
 class ActMLP(FeedForward):
-    """y = W_down act(W_up h), no gate and no bias; ``act``: "gelu_tanh" or "gelu" (the erf form).  The activation runs
-    in the first product's epilogue where the kernel has one."""
+    """y = W_down act(W_up h), no gate and no bias; ``act``: "gelu_tanh", "gelu" (the erf form) or "relu2" (the square of
+    relu).  The activation runs in the first product's epilogue where the kernel has one."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, act: str = "gelu_tanh"):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)

@@ -28,7 +28,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, shape: Tuple[int, ...], kind: str, seed: int,
                   init_std: Optional[float] = None, device: str = "cpu") -> torch.Tensor:
     """``kind``: "matrix" ([out, in]), "embedding", "norm" (a vector of scales around one), "norm_offset"
-    (a vector of scales stored around zero) or "vector" (free numbers of order one, e.g. softmax sinks)."""
+    (a vector of scales stored around zero), "vector" (free numbers of order one, e.g. softmax sinks), "fraction"
+    (numbers in [0, 1), e.g. a mixing weight) or "near_identity" (a square matrix: the identity plus N(0, 0.1))."""
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if kind == "norm":
@@ -37,6 +38,11 @@ def random_tensor(name: str, shape: Tuple[int, ...], kind: str, seed: int,
         t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 0.4 - 0.2
     elif kind == "vector":
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
+    elif kind == "fraction":
+        t = torch.rand(shape, generator=g, device=device, dtype=torch.float32)
+    elif kind == "near_identity":
+        t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.1
+        t += torch.eye(shape[-2], shape[-1], device=device, dtype=torch.float32)
     elif kind == "embedding":
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
         t *= 1.0 if init_std is None else init_std
