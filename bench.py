@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun|ripesun]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun|ripesun|botalorn]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
@@ -468,6 +468,108 @@ def ripesun_workload(only: str = "") -> int:
     return 0
 
 
+def _botalorn_config(width, heads, kv, dim, vdim, window, taps, streams, ff, layers, vocab):
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": dim, "vdim": vdim, "conv": taps},
+             "mlp": {"kind": "dense", "ff": ff}}
+    attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": taps, "scale": dim ** -0.5, "mask": {"size": window}}
+    pattern, out, first = ("delta", "delta", "attention", "delta", "delta", "shared"), [], None
+    for i in range(layers):
+        kind = pattern[i % len(pattern)]
+        if kind == "delta":
+            out.append(delta)
+        elif kind == "attention" or first is None:
+            first = i if first is None else first
+            out.append({"type": "attention", "mixer": dict(attn), "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            out.append({"type": "attention", "mixer": dict(attn, kv_from=first), "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Botalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "streams": streams, "layers": out}
+
+
+# (name, Botalorn sizes); layers follow the pattern delta, delta, attention, delta, delta, attention reading the first
+# one's cache.  Beside each: the Ripesun model of the same width, heads, head sizes, window, feed-forward size, layers and
+# vocabulary (its pattern: linear attention, gated recurrence, latent attention), and the dense Qwen3-style model of equal
+# per-token feed-forward arithmetic (3 * I = 2 * ff).
+BOTALORN_SHAPES = (
+    ("w2048_h16", dict(width=2048, heads=16, kv=4, dim=128, vdim=128, window=1024, taps=4, streams=4, ff=6144, layers=6, vocab=32768)),
+    ("w4096_h32", dict(width=4096, heads=32, kv=8, dim=128, vdim=128, window=2048, taps=4, streams=4, ff=12288, layers=3, vocab=32768)),
+    ("w1024_h16", dict(width=1024, heads=16, kv=4, dim=64, vdim=64, window=256, taps=4, streams=2, ff=3072, layers=6, vocab=32768)),
+)
+
+
+def botalorn_workload(only: str = "") -> int:
+    """Prefill and decode throughput of the Botalorn design at a few sizes that resemble a real model's layers (random
+    bfloat16 weights), each beside the Ripesun model and the dense Qwen3-style model of equal size.  Prefill: one prompt
+    of 2,048 tokens; decode: 8 and 64 requests at 1,024 tokens of context, captured graphs.  Timed on the device with CUDA
+    events after warm-up; every step reads more weights than L2 holds.  The timed steps lie between cudaProfilerStart and
+    cudaProfilerStop."""
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
+    results = []
+    P, CTX = 2048, 1024
+    for name, sz in BOTALORN_SHAPES:
+        if only and only != name:
+            continue
+        inter = int(round(2 * sz["ff"] / 3 / 256)) * 256
+        dense = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=sz["layers"], hidden_size=sz["width"],
+                     num_attention_heads=sz["heads"], num_key_value_heads=sz["kv"], head_dim=sz["dim"], intermediate_size=inter,
+                     vocab_size=sz["vocab"], rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                     max_position_embeddings=8192, hidden_act="silu", attention_bias=False, eos_token_id=0)
+        ripesun = _ripesun_config(width=sz["width"], heads=sz["heads"], dim=sz["dim"], vdim=sz["vdim"], rot=sz["dim"] // 2,
+                                  kv_rank=4 * sz["dim"], q_rank=12 * sz["dim"], window=sz["window"], gru=sz["width"], ff=sz["ff"],
+                                  side=sz["width"] // 16, layers=sz["layers"], vocab=sz["vocab"])
+        row = {"shape": name, "sizes": dict(sz), "dense_intermediate": inter}
+        for which, cfg in (("botalorn", _botalorn_config(**sz)), ("ripesun", ripesun), ("dense", dense)):
+            ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=64 * (CTX + 64) + P + 64, max_requests=64,
+                              max_batch_tokens=P, max_context=4096, max_batch_size=64)
+            eng = Engine.from_config(cfg, seed=5, engine_config=ec, init_std=0.02, device_init=True)
+            V = sz["vocab"]
+            toks = lambda n, s: [(7 * i + 13 * s) % V for i in range(n)]
+
+            def timed(fn, warm, reps):
+                for i in range(warm):
+                    fn(i)
+                torch.cuda.synchronize()
+                ms = []
+                for i in range(reps):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn(warm + i)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms.append(e0.elapsed_time(e1))
+                return sorted(ms)[len(ms) // 2]
+
+            def prefill(i):
+                eng.step([(9000 + i, toks(P, i), [P - 1])])
+                eng.end_request(9000 + i)
+
+            out = {}
+            torch.cuda.profiler.start()
+            t = timed(prefill, 3, 5)
+            out["prefill_2048"] = {"ms": round(t, 3), "tokens_per_s": round(P / t * 1e3, 1)}
+            for batch in (8, 64):
+                for r in range(0, batch, 2):
+                    eng.step([(r, toks(CTX, r), []), (r + 1, toks(CTX, r + 1), [])])
+                t = timed(lambda i: eng.step([(r, [(i + r) % V], [0]) for r in range(batch)]), 4, 12)
+                out[f"decode_b{batch}"] = {"ms": round(t, 3), "tokens_per_s": round(batch / t * 1e3, 1)}
+                for r in range(batch):
+                    eng.end_request(r)
+            torch.cuda.profiler.stop()
+            eng.check_waits()
+            out["wait_errors"] = sum(1 for w in K.read_wait_errors() if w != 0)
+            row[which] = out
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    print(json.dumps({"metric": "botalorn_beside_ripesun_and_dense", "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+                      "dtype": "bf16", "data": "synthetic", "impl": "ours", "shapes": results,
+                      "config": {"prefill_tokens": P, "decode_context": CTX, "page_size": 16, "seed": 5,
+                                 "l2": "weights read per step exceed L2"}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -486,17 +588,17 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=0, help="top-k of the end-to-end run")
     ap.add_argument("--align-step-tokens", type=int, default=0,
                     help="serving workload: the scheduler cuts portions so that a step's tokens fill whole tiles of this many rows")
-    ap.add_argument("--shape", default="", help="dulisun and ripesun workloads: only this shape (default: all)")
+    ap.add_argument("--shape", default="", help="dulisun, ripesun and botalorn workloads: only this shape (default: all)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun", "ripesun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun", "ripesun", "botalorn"],
                     help="decode: the headline decode-step measurement (Qwen3-8B shape, 1,024-token prompts); llama3_8b: the same "
                          "line for the Llama-3-8B shape, 16 requests at contexts ending at 8,192 tokens; serving: continuous batching "
                          "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each); "
                          "mixed_step: one step of a 512-token portion beside 24 decoding requests on that shape, timed alone; "
                          "dulisun: prefill and decode of the Dulisun design at a few sizes beside the dense model of equal size; "
-                         "ripesun: the same for the Ripesun design")
+                         "ripesun: the same for the Ripesun design; botalorn: the Botalorn design beside Ripesun and the dense model")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -518,6 +620,8 @@ def main() -> int:
         return dulisun_workload(args.shape)
     if args.workload == "ripesun":
         return ripesun_workload(args.shape)
+    if args.workload == "botalorn":
+        return botalorn_workload(args.shape)
 
     import numpy as np
     import torch

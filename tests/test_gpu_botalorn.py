@@ -1,0 +1,727 @@
+"""The Botalorn design in the engine against its plain implementation (``plain_botalorn``): each mechanism alone, then
+whole models under every way of cutting the work, in float32 and bfloat16.
+
+The configurations are small and differ from one another in every size and constant: one to five streams (and none),
+head counts with and without groups, key and value sizes that differ, convolutions of one to five taps, windows of less
+than a page, of several pages and none, two layers that share one cache under different windows, layers without a
+feed-forward, models of one kind of mixer only.  Where random weights would hide a fault the inputs are made so that it
+shows: keys just inside and just outside a window and at position 0 are scaled until their scores stand out; a decay is
+made so slow that the first token still matters after hundreds.
+"""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_botalorn as pb
+
+pytestmark = pytest.mark.gpu
+
+
+def _attn(heads, kv, dim, vdim, window, scale, taps, kv_from=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": taps, "scale": scale, "mask": {"size": window} if window else None}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _delta(heads, kv, dim, vdim, taps):
+    return {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": taps}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+CONFIGS = {
+    # three streams; six heads in two groups, keys of 24 and values of 16; windows of 21 and 9 on one shared cache; a layer without feed-forward
+    "A": {"architecture": "Botalorn", "vocab": 333, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0}, "streams": 3, "layers": [
+        {"type": "delta", "mixer": _delta(3, 1, 20, 12, 4), "mlp": _dense(80)},
+        {"type": "attention", "mixer": _attn(6, 2, 24, 16, 21, 0.2, 3), "mlp": _dense(64)},
+        {"type": "delta", "mixer": _delta(2, 2, 16, 40, 2), "mlp": None},
+        {"type": "attention", "mixer": _attn(6, 2, 24, 16, 9, 0.3, 5, kv_from=1), "mlp": _dense(48)},
+        {"type": "attention", "mixer": _attn(2, 1, 8, 8, 40, 0.35, 1), "mlp": None}]},
+    # no stream tensors at all (the plain residual sum), no embedding scale; one head; no mask (every key stays) and a reader of that cache
+    "B": {"architecture": "Botalorn", "vocab": 257, "width": 64, "norm": {"eps": 3e-6}, "layers": [
+        {"type": "delta", "mixer": _delta(1, 1, 32, 32, 1), "mlp": _dense(96)},
+        {"type": "attention", "mixer": _attn(1, 1, 16, 24, 0, 0.25, 4), "mlp": None},
+        {"type": "attention", "mixer": _attn(1, 1, 16, 24, 0, 0.35, 2, kv_from=1), "mlp": _dense(72)}]},
+    # sizes the tensor-core kernels take; 16 heads over 4, heads of 64 and of 128 / 64; windows of four pages and of one; five streams
+    "C": {"architecture": "Botalorn", "vocab": 512, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 8.0}, "streams": 5, "layers": [
+        {"type": "attention", "mixer": _attn(16, 4, 64, 64, 64, 0.125, 4), "mlp": _dense(256)},
+        {"type": "delta", "mixer": _delta(4, 2, 64, 64, 4), "mlp": _dense(256)},
+        {"type": "delta", "mixer": _delta(2, 2, 128, 32, 3), "mlp": _dense(128)},
+        {"type": "attention", "mixer": _attn(4, 4, 128, 64, 16, 0.09, 2), "mlp": _dense(128)}]},
+    # the delta rule only (no paged cache group); sizes no vector kernel takes: width 90, heads of 10 / 6, one stream with tensors
+    "D": {"architecture": "Botalorn", "vocab": 101, "width": 90, "norm": {"eps": 1e-5}, "streams": 1, "layers": [
+        {"type": "delta", "mixer": _delta(3, 3, 10, 6, 3), "mlp": _dense(30)},
+        {"type": "delta", "mixer": _delta(4, 1, 6, 10, 2), "mlp": None},
+        {"type": "delta", "mixer": _delta(1, 1, 130, 8, 4), "mlp": _dense(22)}]},
+    # attention only (no recurrent state beside the convolutions'), odd sizes, windows of 5 and 33 on caches of their own; two streams
+    "E": {"architecture": "Botalorn", "vocab": 130, "width": 70, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5}, "streams": 2, "layers": [
+        {"type": "attention", "mixer": _attn(3, 3, 10, 14, 5, 0.4, 2), "mlp": _dense(50)},
+        {"type": "attention", "mixer": _attn(4, 2, 6, 6, 33, 0.5, 4), "mlp": None}]},
+}
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 8}
+LENGTHS = {"A": [1, 9, 50, 131], "B": [2, 20, 77], "C": [5, 70, 150], "D": [3, 40, 90], "E": [2, 41, 95]}
+FP32_TOL, BF16_TOL = 1e-4, 4e-2
+DTYPES = [("float32", FP32_TOL), ("bfloat16", BF16_TOL)]
+
+
+def load_plain(folder):
+    from aien_sovereign_core_mv_b200.weights.safetensors_io import CheckpointFiles
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    files = CheckpointFiles(folder)
+    tensors = {n: files.tensor(n).float().numpy().astype(np.float64) for n in files.names()}
+    files.close()
+    return cfg, tensors
+
+
+def tokens(which, n, seed):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, CONFIGS[which]["vocab"], n)]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    from aien_sovereign_core_mv_b200 import write_random_model
+    root = tmp_path_factory.mktemp("botalorn")
+    out = {}
+    for i, which in enumerate(CONFIGS):
+        d = write_random_model(os.path.join(str(root), which), CONFIGS[which], 40 + i)
+        cfg, tensors = load_plain(d)
+        reqs = {j + 1: tokens(which, n, 100 * i + n) for j, n in enumerate(LENGTHS[which])}
+        want = {rid: pb.forward(cfg, tensors, toks) for rid, toks in reqs.items()}
+        out[which] = (d, reqs, want)
+    return out
+
+
+def check(collected, want, tol, what):
+    assert collected, f"{what}: nothing was collected"
+    for rid, rows in collected.items():
+        pos = sorted(rows)
+        got, ref = np.stack([rows[p] for p in pos]), want[rid][pos]
+        H.assert_close(got, ref, tol, f"{what} request {rid} (positions {pos[0]}..{pos[-1]})")
+
+
+def make_ctx(dtype, positions, seq_of_token, q_start, ctx_len, groups=()):
+    from test_gpu_parts import make_ctx as mk
+    return mk(dtype, positions, seq_of_token, q_start, ctx_len, groups)
+
+
+def i32(a):
+    return torch.tensor(a, dtype=torch.int32, device="cuda")
+
+
+def f64(t):
+    return t.double().cpu().numpy()
+
+
+# ------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("width,scale", [(64, 1.0), (90, 12.0), (37, 0.5)])
+def test_embedding_with_the_position_vector(width, scale):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(width)
+    table = torch.randn(50, width, generator=g).to(torch.bfloat16)
+    ids = [3, 49, 0, 7, 7, 21]
+    positions = [0, 1, 2, 63, 4097, 70001]                       # far positions: the angle is not taken in 16 or 32 bits
+    inv = torch.tensor([pb.SINUSOID_BASE ** (-2.0 * i / width) for i in range((width + 1) // 2)], dtype=torch.float64).cuda()
+    x = torch.zeros(len(ids), width, dtype=torch.float32).cuda()
+    K.embed_gather_sinusoid(table.cuda(), i32(ids), i32(positions), inv, x, scale)
+    want = table.double().numpy()[ids] * scale + pb.sinusoid(positions, width)
+    H.assert_close(x.cpu().numpy(), want, 2e-6, "embedding")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,width", [(1, 48), (3, 70), (4, 256), (8, 33)])
+def test_streams_write_read_and_norm(dtype, n, width):
+    """The write of the sublayer before (from one output and from partial products), the read and its norm, in one kernel;
+    then the sum of the streams of chosen rows after a pending write."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(n * width)
+    T, eps = 13, 1e-5
+    xs = torch.randn(n, T, width, generator=g)
+    packs = [torch.cat([torch.randn(n, generator=g), torch.randn(n, generator=g), (torch.eye(n) + 0.3 * torch.randn(n, n, generator=g)).reshape(-1)])
+             for _ in range(2)]
+    w = (torch.rand(width, generator=g) + 0.5).to(dtype)
+    parts = torch.randn(3, T, width, generator=g)
+    for y in (None, parts.sum(0).to(dtype), parts):
+        x = xs.clone().cuda()
+        h = torch.zeros(T, width, dtype=dtype).cuda()
+        K.hc_norm(x, None if y is None else y.cuda(), None if y is None else packs[0].cuda(), packs[1].cuda(), w.cuda(), eps, h)
+        new = f64(xs)
+        if y is not None:
+            yy = f64(y) if y.dim() == 2 else f64(y).sum(0)
+            new = pb.stream_write(new, yy, f64(packs[0][2 * n:]).reshape(n, n), f64(packs[0][n:2 * n]))
+        want = pb.rms(pb.stream_read(new, f64(packs[1][:n])), eps) * f64(w)
+        tol = 2e-6 if dtype == torch.float32 else 6e-3
+        H.assert_close(x.cpu().numpy(), new, 2e-6, "streams after the write")
+        H.assert_close(h.float().cpu().numpy(), want, tol, "normed read")
+    rows = [12, 0, 5, 5]
+    out = torch.zeros(len(rows), width, dtype=torch.float32).cuda()
+    K.hc_sum_rows(xs.cuda(), parts.cuda(), packs[0].cuda(), i32(rows), out)
+    new = pb.stream_write(f64(xs), f64(parts).sum(0), f64(packs[0][2 * n:]).reshape(n, n), f64(packs[0][n:2 * n]))
+    H.assert_close(out.cpu().numpy(), new.sum(0)[rows], 2e-6, "sum of the streams")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_shift_across_portions_single_tokens_and_slots(dtype):
+    """Two requests: portions of 5, 2 and the rest, then single tokens inside the read-and-norm kernel; the row before a
+    portion comes from the request's slot, zeros at position 0 whatever the slot held."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(9)
+    W, lens = 52, [19, 11]
+    hn = [torch.randn(n, W, generator=g) for n in lens]
+    sw = torch.rand(W, generator=g).to(dtype)
+    want = [pb.token_shift(f64(a), f64(sw)) for a in hn]
+    state = torch.full((4, W), 3.25, dtype=torch.float32).cuda()
+    slots = [2, 0]
+    got = [[], []]
+    at = [0, 0]
+    for sizes in ([5, 4], [2, 1], [8, 3]):
+        rows = torch.cat([hn[s][at[s]:at[s] + n] for s, n in enumerate(sizes)]).cuda()
+        pos = sum([list(range(at[s], at[s] + n)) for s, n in enumerate(sizes)], [])
+        sot = sum([[s] * n for s, n in enumerate(sizes)], [])
+        out = torch.zeros(sum(sizes), W, dtype=dtype).cuda()
+        K.token_shift(rows, sw.cuda(), state, i32(slots), i32(sot), i32([0, sizes[0], sum(sizes)]), i32(pos), out)
+        got[0].append(out[:sizes[0]].float().cpu().numpy()); got[1].append(out[sizes[0]:].float().cpu().numpy())
+        at = [at[s] + n for s, n in enumerate(sizes)]
+    # the rest one token a step through the fused kernel: one stream, in = 1, norm weight 1 and rows that already have unit mean square
+    pack = torch.ones(3, dtype=torch.float32).cuda()
+    ones = torch.ones(W, dtype=torch.float32).cuda()
+    while at[0] < lens[0]:
+        live = [s for s in (0, 1) if at[s] < lens[s]]
+        rows = torch.stack([hn[s][at[s]] for s in live])
+        rows = rows / rows.pow(2).mean(-1, keepdim=True).sqrt()
+        for s, r in zip(live, rows):
+            hn[s][at[s]] = r
+        out = torch.zeros(len(live), W, dtype=dtype).cuda()
+        K.hc_norm(rows.unsqueeze(0).contiguous().cuda(), None, None, pack, ones, 0.0, out, sw.cuda(), state, i32([slots[s] for s in live]),
+                  i32([at[s] for s in live]))
+        for j, s in enumerate(live):
+            got[s].append(out[j:j + 1].float().cpu().numpy())
+            at[s] += 1
+    want = [pb.token_shift(f64(a), f64(sw)) for a in hn]
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    for s in (0, 1):
+        H.assert_close(np.concatenate(got[s]), want[s], tol, f"shifted rows of request {s}")
+    assert float((state[1] - 3.25).abs().max()) == 0.0 and float((state[3] - 3.25).abs().max()) == 0.0
+    H.assert_close(state[2].cpu().numpy(), f64(hn[0][-1]), 2e-6, "the slot holds the last row as it was before the shift")
+
+
+def _paged(tables, page, rows_k, rows_v, dtype, slots=64):
+    """Caches [slots * page, ...] whose pages lie in the scrambled order of ``tables``; rows_*[s] are request s's rows by position."""
+    k = torch.full((slots * page,) + tuple(rows_k[0].shape[1:]), float("nan"), dtype=dtype)
+    v = torch.full((slots * page,) + tuple(rows_v[0].shape[1:]), float("nan"), dtype=dtype)
+    for s, tab in enumerate(tables):
+        for p in range(rows_k[s].shape[0]):
+            at = tab[p // page] * page + p % page
+            k[at], v[at] = rows_k[s][p].to(dtype), rows_v[s][p].to(dtype)
+    width = max(len(t) for t in tables)
+    bt = torch.full((len(tables), width), -1, dtype=torch.int32)
+    for s, tab in enumerate(tables):
+        bt[s, :len(tab)] = torch.tensor(tab)
+    return k.cuda(), v.cuda(), bt.cuda(), width
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,page,heads,kv,dim,vdim", [(5, 8, 3, 3, 10, 14), (16, 16, 4, 1, 32, 32), (37, 8, 6, 2, 24, 16),
+                                                             (0, 16, 2, 1, 64, 40), (64, 16, 8, 2, 128, 64), (1, 8, 1, 1, 8, 8)])
+def test_biased_attention_at_the_edges_of_its_window(dtype, window, page, heads, kv, dim, vdim):
+    """Keys are made to grow toward the past faster than the distance bias falls, so the oldest key a query may see takes
+    nearly all the weight: one position more or less in the window, or a lost key at position 0 of a prompt without a
+    window, changes the whole output.  Queries stand in a portion of a prompt (across page borders) and alone (decoding);
+    a second request shares the step."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(window * 7 + dim)
+    lens = [150, 41]
+    scale = dim ** -0.5
+    temp = (torch.rand(heads, generator=g) + 0.75)
+    slope = torch.tensor(pb.slopes(heads), dtype=torch.float32)
+    u = torch.randn(kv, dim, generator=g)
+    u = u / u.norm(dim=-1, keepdim=True)
+    ks, vs, qs = [], [], []
+    for n in lens:
+        grow = (3.0 + float(slope.max())) / (scale * 0.75)          # per position, more than any head's bias takes off
+        amp = (n - torch.arange(n, dtype=torch.float32)) * grow / 4.0
+        ks.append((u[None] * amp[:, None, None] / 4.0 + 0.05 * torch.randn(n, kv, dim, generator=g)).to(dtype).float())
+        vs.append(torch.randn(n, kv, vdim, generator=g).to(dtype).float())
+        qs.append((u.repeat_interleave(heads // kv, 0)[None] * 16.0 + 0.05 * torch.randn(n, heads, dim, generator=g)).to(dtype).float())
+    tables = [[7, 2, 11, 0, 5, 9, 13, 1, 3, 20, 21, 4, 6, 8, 10, 12, 14, 15, 16][: (lens[0] + page - 1) // page],
+              [30, 25, 31, 22, 23, 24][: (lens[1] + page - 1) // page]]
+    kc, vc, bt, width = _paged(tables, page, ks, vs, dtype)
+    gate = torch.randn(sum(lens), heads + 3, generator=g)
+
+    def plain(s, lo, hi, grow_rows):
+        pos = list(range(lens[s]))
+        o = pb.biased_window_attention(f64(qs[s][lo:hi]), f64(ks[s]), f64(vs[s]), pos[lo:hi], pos, scale, f64(temp), window, f64(slope))
+        return o * pb.sigmoid(f64(grow_rows[:, :heads]))[:, :, None]
+
+    def run(entries):                                              # (request, first position, count)
+        pos, sot, rows, gr = [], [], [], []
+        for i, (s, p0, n) in enumerate(entries):
+            pos += list(range(p0, p0 + n)); sot += [i] * n
+            rows.append(qs[s][p0:p0 + n].reshape(n, heads * dim))
+            gr.append(gate[sum(lens[:s]) + p0: sum(lens[:s]) + p0 + n])
+        q = torch.cat(rows).to(dtype).cuda()
+        out = torch.zeros(len(pos), heads * vdim, dtype=dtype).cuda()
+        table = torch.stack([bt[s] for s, _, _ in entries])
+        K.paged_attention_generic(q, kc, vc, table, width, i32(sot), i32(pos), out, heads, kv, dim, page, window, scale, value_dim=vdim,
+                                  head_scale=temp.cuda(), slopes=slope.cuda(), gate=torch.cat(gr).contiguous().cuda())
+        want = np.concatenate([plain(s, p0, p0 + n, g_) for (s, p0, n), g_ in zip(entries, gr)])
+        tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+        H.assert_close(out.float().cpu().numpy().reshape(len(pos), heads, vdim), want, tol, f"window {window}, entries {entries}")
+
+    run([(0, 0, 150), (1, 0, 41)])                                 # whole prompts: the first tokens, every page border
+    run([(0, 60, 70), (1, 40, 1)])                                 # a portion in the middle beside a single token
+    run([(0, 149, 1), (1, 17, 1)])                                 # single tokens (decoding)
+    run([(1, 7, 2), (0, 127, 3)])                                  # two tokens before a page border, three across one
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps,heads,kv,dim,vdim,own", [(3, 6, 2, 24, 16, True), (1, 2, 1, 8, 8, True), (5, 4, 4, 10, 14, True), (4, 3, 1, 16, 32, False)])
+def test_convolution_norms_and_cache_rows_of_the_attention(dtype, taps, heads, kv, dim, vdim, own):
+    """q, k, v of two requests through the convolution and the norms in one step and in portions (2, 1, 1, 3, the rest)
+    through state slots that held something else: q equals the plain rows, and the cache holds the plain keys and values."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(taps * 100 + dim)
+    eps, lens = 1e-5, [23, 9]
+    Cq, Ck, Cv = heads * dim, (kv * dim if own else 0), (kv * vdim if own else 0)
+    C = Cq + Ck + Cv
+    proj = [torch.randn(n, C + heads, generator=g) for n in lens]             # the gate's columns follow and stay untouched
+    wq, wk, wv = (torch.randn(c, taps, generator=g).to(dtype) for c in (Cq, max(Ck, 1), max(Cv, 1)))
+    qn, kn = ((torch.rand(c, generator=g) + 0.5).to(dtype) for c in (Cq, max(Ck, 1)))
+    want_q, want_k, want_v = [], [], []
+    for p in proj:
+        a = f64(p)
+        want_q.append(pb.rms(pb.causal_conv(a[:, :Cq], f64(wq)), eps) * f64(qn))
+        if own:
+            want_k.append(pb.rms(pb.causal_conv(a[:, Cq:Cq + Ck], f64(wk)), eps) * f64(kn))
+            v = pb.causal_conv(a[:, Cq + Ck:C], f64(wv))
+            want_v.append(pb.rms(v.reshape(-1, kv, vdim), eps).reshape(-1, Cv))
+    state = torch.full((4, max(1, (taps - 1) * C)), 5.5, dtype=torch.float32).cuda()
+    kc = torch.zeros(64, kv, dim, dtype=dtype).cuda()
+    vc = torch.zeros(64, kv, vdim, dtype=dtype).cuda()
+    place = [[40 + p for p in range(lens[0])], [30 - p for p in range(lens[1])]]
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+
+    def run(entries, slots):
+        pos, sot, qs_, rows, kvs = [], [], [0], [], []
+        for i, (s, p0, n) in enumerate(entries):
+            pos += list(range(p0, p0 + n)); sot += [i] * n; qs_.append(qs_[-1] + n)
+            rows.append(proj[s][p0:p0 + n]); kvs += place[s][p0:p0 + n]
+        q = torch.zeros(len(pos), Cq, dtype=dtype).cuda()
+        K.attn_conv_prepare(torch.cat(rows).cuda(), 0, Cq, Cq + Ck, Cq, Ck, Cv, wq.cuda(), wk.cuda() if own else None, wv.cuda() if own else None,
+                            taps, qn.cuda(), kn.cuda() if own else None, eps, kv, vdim, True, state if taps > 1 else None,
+                            i32(slots) if taps > 1 else i32(qs_), i32(sot), i32(qs_), i32(pos), i32(kvs) if own else None,
+                            kc if own else None, vc if own else None, q)
+        return q.float().cpu().numpy()
+
+    def cached(s):
+        idx = torch.tensor(place[s]).cuda()
+        return kc[idx].float().cpu().numpy().reshape(lens[s], -1), vc[idx].float().cpu().numpy().reshape(lens[s], -1)
+
+    got = run([(0, 0, lens[0]), (1, 0, lens[1])], [3, 1])
+    H.assert_close(got, np.concatenate(want_q), tol, "q of two requests in one step")
+    if own:
+        for s in (0, 1):
+            k_, v_ = cached(s)
+            H.assert_close(k_, want_k[s], tol, f"cached keys of request {s}"); H.assert_close(v_, want_v[s], tol, f"cached values of request {s}")
+        kc.zero_(); vc.zero_()
+    if taps > 1:
+        assert float((state[0] - 5.5).abs().max()) == 0.0 and float((state[2] - 5.5).abs().max()) == 0.0
+    at, out = 0, []
+    for n in [2, 1, 1, 3, lens[0] - 7]:                            # slot 1 holds the second request's rows: position 0 starts from zeros
+        out.append(run([(0, at, n)], [1]))
+        at += n
+    H.assert_close(np.concatenate(out), want_q[0], tol, "q in portions")
+    if own:
+        k_, v_ = cached(0)
+        H.assert_close(k_, want_k[0], tol, "cached keys, portions"); H.assert_close(v_, want_v[0], tol, "cached values, portions")
+
+
+@pytest.mark.parametrize("taps,heads,qk,dim,vdim,slow", [(4, 3, 1, 20, 12, False), (1, 2, 2, 16, 40, True), (3, 4, 2, 64, 64, True), (2, 1, 1, 130, 8, False),
+                                                         (3, 6, 3, 32, 64, False), (5, 4, 1, 6, 10, True)])
+def test_delta_rule_in_one_step_in_pieces_and_token_by_token(taps, heads, qk, dim, vdim, slow):
+    """Convolution, silu, unit vectors, decay and beta, then the recurrence: two requests of unequal length in one step;
+    the first again in pieces (33, 1, 1, 2, the rest) through a slot another request used; both token by token.  ``slow``:
+    decays so near 1 that the first tokens still weigh in the state after hundreds (a state that is dropped or zeroed
+    between steps shows at once)."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(taps * 1000 + dim)
+    lens = [210, 6]
+    QK, Vv = qk * dim, heads * vdim
+    C = 2 * QK + Vv
+    proj = [torch.randn(n, C + Vv + 2 * heads, generator=g) for n in lens]     # q | k | v | (gate, untouched) | b | a
+    b_off = C + Vv
+    wq, wk, wv = (torch.randn(c, taps, generator=g) * 0.6 for c in (QK, QK, Vv))
+    a_log = (torch.full((heads,), -7.0) if slow else torch.randn(heads, generator=g) - 1.0)
+    dt_bias = torch.randn(heads, generator=g)
+    m = {"heads": heads, "kv_heads": qk, "dim": dim, "vdim": vdim}
+
+    def inputs(s):
+        a = f64(proj[s])
+        q = pb.silu(pb.causal_conv(a[:, :QK], f64(wq))).reshape(-1, qk, dim)
+        k = pb.silu(pb.causal_conv(a[:, QK:2 * QK], f64(wk))).reshape(-1, qk, dim)
+        v = pb.silu(pb.causal_conv(a[:, 2 * QK:C], f64(wv))).reshape(-1, heads, vdim)
+        q = q / np.sqrt((q * q).sum(-1, keepdims=True) + pb.UNIT_EPS) * dim ** -0.5
+        k = k / np.sqrt((k * k).sum(-1, keepdims=True) + pb.UNIT_EPS)
+        beta = pb.sigmoid(a[:, b_off:b_off + heads])
+        decay = np.exp(-np.exp(f64(a_log))[None] * pb.softplus(a[:, b_off + heads:b_off + 2 * heads] + f64(dt_bias)[None]))
+        return q, k, v, beta, decay
+
+    want, S_want = zip(*(pb.delta_recurrence(*inputs(s)) for s in (0, 1)))
+    conv_n = (taps - 1) * C
+    state = torch.full((4, conv_n + heads * dim * vdim), 2.5, dtype=torch.float32).cuda()
+
+    def run(entries, slots):
+        pos, sot, qs_, rows = [], [], [0], []
+        for i, (s, p0, n) in enumerate(entries):
+            pos += list(range(p0, p0 + n)); sot += [i] * n; qs_.append(qs_[-1] + n); rows.append(proj[s][p0:p0 + n])
+        T = len(pos)
+        qkv = torch.zeros(T, C, dtype=torch.float32).cuda()
+        gb = torch.zeros(T, 2 * heads, dtype=torch.float32).cuda()
+        K.delta_conv_prepare(torch.cat(rows).cuda(), 0, QK, 2 * QK, b_off, b_off + heads, qk, dim, heads, vdim, wq.cuda(), wk.cuda(), wv.cuda(),
+                             taps, a_log.cuda(), dt_bias.cuda(), state, i32(slots), i32(sot), i32(qs_), i32(pos), qkv, gb)
+        o = torch.zeros(T, Vv, dtype=torch.float32).cuda()
+        K.delta_rule(qkv, 0, QK, 2 * QK, gb, state, conv_n, i32(slots), i32(qs_), i32(pos), o, len(entries), heads, qk, dim, vdim)
+        return o.cpu().numpy().reshape(T, heads, vdim)
+
+    S_of = lambda slot: state[slot, conv_n:].cpu().numpy().reshape(heads, dim, vdim)
+    got = run([(0, 0, lens[0]), (1, 0, lens[1])], [2, 0])
+    H.assert_close(got, np.concatenate(want), 3e-5, "two requests in one step")
+    H.assert_close(S_of(2), S_want[0], 3e-5, "state of the first"); H.assert_close(S_of(0), S_want[1], 3e-5, "state of the second")
+    assert float((state[1] - 2.5).abs().max()) == 0.0 and float((state[3] - 2.5).abs().max()) == 0.0
+    if slow and dim >= 16:                                         # what came long before still weighs: without it the output is another
+        late, _ = pb.delta_recurrence(*(a[-20:] for a in inputs(0)))
+        assert np.abs(late[-1] - want[0][-1]).max() > 1e-2 * np.abs(want[0][-1]).max()
+    at, out = 0, []
+    for n in [33, 1, 1, 2, lens[0] - 37]:
+        out.append(run([(0, at, n)], [0]))                         # slot 0 holds the second request's state
+        at += n
+    H.assert_close(np.concatenate(out), want[0], 3e-5, "the same tokens in pieces")
+    H.assert_close(S_of(0), S_want[0], 3e-5, "state after the pieces")
+    outs = [[], []]
+    for i in range(lens[1]):
+        o = run([(0, i, 1), (1, i, 1)], [3, 1])
+        outs[0].append(o[0]); outs[1].append(o[1])
+    H.assert_close(np.stack(outs[0]), want[0][:lens[1]], 3e-5, "token by token, first request")
+    H.assert_close(np.stack(outs[1]), want[1], 3e-5, "token by token, second request")
+    H.assert_close(S_of(1), S_want[1], 3e-5, "state after single tokens")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("groups,group,act", [(3, 12, "silu"), (1, 130, "silu"), (6, 64, "sigmoid")])
+def test_norm_per_head_with_a_shared_weight_and_gate(dtype, groups, group, act):
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(group)
+    T, eps = 7, 1e-5
+    o = torch.randn(T, groups * group, generator=g) * 3.0
+    gate = torch.randn(T, groups * group + 5, generator=g)
+    w = (torch.rand(group, generator=g) + 0.5).to(dtype)
+    out = torch.zeros(T, groups * group, dtype=dtype).cuda()
+    K.grouped_gated_rmsnorm(o.cuda(), gate.cuda()[:, 2:2 + groups * group], w.cuda(), eps, out, group, act)
+    z = f64(gate[:, 2:2 + groups * group])
+    want = (pb.rms(f64(o).reshape(T, groups, group), eps) * f64(w)).reshape(T, -1) * (pb.silu(z) if act == "silu" else pb.sigmoid(z))
+    H.assert_close(out.float().cpu().numpy(), want, 3e-6 if dtype == torch.float32 else 8e-3, "norm per head")
+
+
+# ------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_layers_of_a_short_request_float32(models, which):
+    """The sum of the streams after every layer, so that a fault names its layer.  A block leaves its last write pending;
+    the sum is taken with it."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    d, reqs, _ = models[which]
+    cfg, tensors = load_plain(d)
+    toks = reqs[2]
+    want = []
+    pb.forward(cfg, tensors, toks, want)
+    eng = H.engine_for(d, "float32", PAGE[which], 256, replay_steps=False)
+    seen = []
+    rows = i32(list(range(len(toks))))
+    for b in eng.model.blocks:
+        def wrapped(ctx, x, delta, run, *a, _inner=b.forward, **kw):
+            out = _inner(ctx, x, delta, run, *a, **kw)
+            total = torch.zeros(len(toks), x.shape[-1], dtype=torch.float32, device=x.device)
+            out.sum_rows(ctx, x, rows, total)
+            seen.append(total)
+            return out
+        b.forward = wrapped
+    eng.step([(1, toks, [0])])
+    assert len(seen) == len(want)
+    for i, (a, w) in enumerate(zip(seen, want)):
+        H.assert_close(a.cpu().numpy(), w, 2e-5, f"{which}: streams after layer {i} ({cfg['layers'][i]['type']})")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_whole_requests(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    steps = [([(rid, toks, list(range(len(toks))))], [rid]) for rid, toks in reqs.items()]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} whole")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_prefill_then_token_by_token(models, which, dtype, tol):
+    """Most of the longest request in one step, then 45 tokens one by one: the decoded tokens' windows pass over the
+    prompt's end, and pages behind a window are given back while the request runs."""
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    toks = reqs[rid]
+    cut = len(toks) - 45
+    steps = [([(rid, toks[:cut], [0, cut - 1])], [])] + [([(rid, [toks[i]], [0])], []) for i in range(cut, len(toks))]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} decode")
+    state = eng.cache_state()
+    assert state["check"] == "" and (which in ("B", "D") or state["metrics"]["window_releases"] > 0)     # B keeps every key, D has none
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_first_tokens_one_by_one(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    steps = [([(rid, [t], [0])], []) for t in reqs[rid][:45]]
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} from the first token")
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_changing_portions(models, which, dtype, tol):
+    d, reqs, want = models[which]
+    eng = H.engine_for(d, dtype, PAGE[which], 512)
+    sizes = [7, 2, 13, 3, 2, 29, 5, 2, 16, 17, 1, 8, 64, 2, 31]
+    for rid, toks in reqs.items():
+        steps, at, k = [], 0, rid
+        while at < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - at)
+            steps.append(([(rid, toks[at:at + n], list(range(n)))], []))
+            at += n
+            k += 1
+        steps[-1] = (steps[-1][0], [rid])
+        check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} portions of request {rid}")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
+
+
+@pytest.mark.parametrize("dtype,tol", DTYPES)
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_mixed_batches_on_few_pages_and_slots(models, which, dtype, tol):
+    """Unequal requests side by side, portions beside single tokens, with three state slots and a pool so small that
+    pages and slots are used again; every logit equals the request's alone."""
+    d, reqs, want = models[which]
+    page = PAGE[which]
+    reqs = dict(reqs)
+    reqs.update({rid + 10: toks[: max(1, len(toks) - 3)] for rid, toks in list(reqs.items())})          # more requests than slots
+    want = dict(want)
+    want.update({rid: want[rid - 10] for rid in reqs if rid > 10})
+    longest = max(len(t) for t in reqs.values())
+    pool = ((longest + page - 1) // page + 6) * page
+    if which == "B":                                               # no mask: every key stays, so the three live requests must fit whole
+        pool = (3 * ((longest + page - 1) // page + 1) + 2) * page
+    eng = H.engine_for(d, dtype, page, pool, max_requests=3)
+    rng = np.random.default_rng(5)
+    at = {rid: 0 for rid in reqs}
+    waiting, live, steps = sorted(reqs, key=lambda r: (len(reqs[r]), r)), [], []
+    held = lambda: sum((at[r] + page - 1) // page + 1 for r in live)
+    while waiting or live:
+        while waiting and len(live) < 3 and (held() + (len(reqs[waiting[0]]) + page - 1) // page + 2) * page <= pool:
+            live.append(waiting.pop(0))
+        if not live:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for rid in list(live):
+            left = len(reqs[rid]) - at[rid]
+            n = 1 if rng.random() < 0.4 else int(min(left, rng.integers(2, 40)))
+            n = min(n, left)
+            if rng.random() < 0.15 and len(live) > 1:
+                continue                                            # a request may sit a step out
+            entries.append((rid, reqs[rid][at[rid]:at[rid] + n], list(range(n))))
+            at[rid] += n
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+                live.remove(rid)
+        if entries:
+            steps.append((entries, end))
+    check(H.run_steps(eng, steps), want, tol, f"{which} {dtype} mixed")
+    state = eng.cache_state()
+    assert state["check"] == "" and state["requests"] == 0
+
+
+def test_a_window_gives_pages_back_and_takes_them_again(models):
+    """A request longer than the pool runs, because only its window is held; a second request then reuses the pages."""
+    d, reqs, want = models["A"]                                     # windows of 21, 9 and 40 positions, pages of 16
+    eng = H.engine_for(d, "float32", 16, 7 * 16, max_requests=2, max_batch_tokens=64)
+    toks = reqs[4]                                                  # 131 tokens through a pool of 112
+    steps, at = [], 0
+    for n in [30, 2, 17, 1, 1, 40, 9, 31]:
+        steps.append(([(4, toks[at:at + n], list(range(n)))], []))
+        at += n
+    assert at == len(toks)
+    steps[-1] = (steps[-1][0], [4])
+    steps.append(([(3, reqs[3], list(range(len(reqs[3]))))], [3]))
+    check(H.run_steps(eng, steps), want, FP32_TOL, "A float32 through a pool smaller than the request")
+    assert eng.cache_state()["check"] == "" and eng.cache_state()["metrics"]["window_releases"] >= 3
+
+
+def test_long_decoding_bfloat16_graphs(models):
+    """130 decode-only steps of two requests (captured graphs, state slots and windows moving on): along the given tokens
+    the logits stay with the plain implementation."""
+    d, reqs, want = models["C"]
+    eng = H.engine_for(d, "bfloat16", 16, 1024)
+    a, b = reqs[3], reqs[2]
+    steps = [([(3, a[:15], [14]), (2, b[:4], [3])], [])]
+    for i in range(min(len(a) - 15, len(b) - 4)):
+        steps.append(([(3, [a[15 + i]], [0]), (2, [b[4 + i]], [0])], []))
+    check(H.run_steps(eng, steps), want, BF16_TOL, "C bfloat16 long decoding")
+    assert len(eng._graphs) > 0                                     # the decode-only steps ran as captured graphs
+
+
+def test_greedy_generation_through_the_entry_point(models):
+    from aien_sovereign_core_mv_b200.engine.generate import generate
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d, reqs, _ = models["A"]
+    cfg, tensors = load_plain(d)
+    prompts = [reqs[2], reqs[3][:30], reqs[1]]
+    n_new = 10
+    want = []
+    for p in prompts:
+        seq, out = list(p), []
+        for _ in range(n_new):
+            t = int(np.argmax(pb.forward(cfg, tensors, seq)[-1]))
+            seq.append(t); out.append(t)
+        want.append(out)
+    eng = H.engine_for(d, "float32", 16, 512, prefill_chunk_size=16, max_prefill_tokens=32)
+    got = generate(eng, prompts, SamplingParams(temperature=0.0, max_tokens=n_new, stop_token_ids=[]))
+    assert got == want
+    assert eng.cache_state()["requests"] == 0 and eng.cache_state()["check"] == ""
+
+
+def test_sampling_and_the_command_line(models):
+    """Sampling through the scheduler (temperature, top-p, top-k) runs and repeats under the same seed; the command line
+    generates the plain implementation's greedy tokens and describes the model."""
+    import subprocess
+    from aien_sovereign_core_mv_b200.engine.generate import Generator
+    from aien_sovereign_core_mv_b200.sampling import SamplingParams
+    d, reqs, _ = models["E"]
+    eng = H.engine_for(d, "bfloat16", 8, 512)
+    params = SamplingParams(temperature=0.8, top_p=0.9, top_k=40, max_tokens=12, stop_token_ids=[], seed=7)
+    a = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    b = Generator(eng).generate([reqs[2], reqs[1]], params, request_ids=[5, 6])
+    assert [r.tokens for r in a] == [r.tokens for r in b] and all(len(r.tokens) == 12 for r in a)
+    cfg, tensors = load_plain(d)
+    seq, want = list(reqs[1]), []
+    for _ in range(5):
+        t = int(np.argmax(pb.forward(cfg, tensors, seq)[-1]))
+        seq.append(t); want.append(t)
+    exe = os.path.join(H.ROOT, "bin", "aien-b200")
+    out = subprocess.run([exe, "generate", "--model-dir", d, "--dtype", "float32", "--prompt-ids", ",".join(map(str, reqs[1])),
+                          "--max-tokens", "5", "--temperature", "0", "--stop-token-ids", "", "--json"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert json.loads(out.stdout.strip().splitlines()[-1])["tokens"] == [want]
+    info = subprocess.run([exe, "info", "--model-dir", d], capture_output=True, text=True, timeout=600)
+    assert info.returncode == 0, info.stderr[-2000:]
+    rec = json.loads(info.stdout.strip().splitlines()[-1])
+    assert rec["architecture"] == "Botalorn" and rec["layers"] == 2 and "window" in rec["cache_groups"] and "state" in rec["cache_groups"]
+
+
+def test_trace_replay_from_the_command(models, tmp_path):
+    d, reqs, want = models["A"]
+    toks = reqs[3]
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:40], "want": [0, 39]}, {"id": 7, "tokens": reqs[1], "want": [0]}], "end": [7]},
+             {"step": 1, "entries": [{"id": "x", "tokens": toks[40:42], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": toks[42:], "want": [len(toks) - 43]}], "end": ["x"]}]
+    out = H.run_trace(d, "float32", str(tmp_path / "out"), 192, steps)
+    assert sorted(out) == [0, 2]
+    H.assert_close(out[0], np.stack([want[3][0], want[3][39], want[1][0]]), FP32_TOL, "trace step 0")
+    H.assert_close(out[2], want[3][-1:], FP32_TOL, "trace step 2")
+
+
+# ------------------------------------------------------------------ configurations drawn at random
+def _random_config(rng):
+    """Sizes, order of layers, windows, sharing of caches, taps, streams and constants drawn at random."""
+    width = rng.choice([64, 72, 96, 128, 160])
+    layers, own = [], []
+    for i in range(rng.randint(3, 7)):
+        kind = rng.choice(["attention", "delta"])
+        mlp = None if rng.random() < 0.2 else _dense(rng.choice([24, 40, 64, 96]))
+        if kind == "attention":
+            j = rng.choice(own) if own and rng.random() < 0.4 else None
+            if j is not None:
+                src = layers[j]["mixer"]
+                heads, kv, dim, vdim = src["heads"], src["kv_heads"], src["dim"], src["vdim"]
+            else:
+                kv = rng.choice([1, 2, 3])
+                heads, dim, vdim = kv * rng.choice([1, 2, 4]), rng.choice([8, 16, 24, 32, 64]), rng.choice([8, 16, 40, 64])
+            window = rng.choice([0, 1, 5, 16, 33, 40, 100])
+            if j is not None and (((layers[j]["mixer"].get("mask") or {}).get("size") or 0) == 0) != (window == 0):
+                window = (layers[j]["mixer"].get("mask") or {}).get("size") or 0          # a cache that keeps all has readers that see all
+            layers.append({"type": kind, "mlp": mlp, "mixer": _attn(heads, kv, dim, vdim, window, rng.choice([0.1, 0.2, dim ** -0.5]),
+                                                                   rng.choice([1, 2, 3, 4]), j)})
+            if j is None:
+                own.append(i)
+        else:
+            qk = rng.choice([1, 2, 3])
+            layers.append({"type": kind, "mlp": mlp, "mixer": _delta(qk * rng.choice([1, 2]), qk, rng.choice([8, 16, 20, 64]), rng.choice([8, 12, 32, 72]),
+                                                                    rng.choice([1, 2, 3, 4]))})
+    cfg = {"architecture": "Botalorn", "vocab": rng.choice([101, 256, 333]), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "embedding": {"scale": rng.choice([1.0, 4.0, 12.0])}, "layers": layers}
+    streams = rng.choice([None, 1, 2, 3, 4, 6])
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Whole prompts, portions of changing size and three requests side by side, against the plain implementation.  float32
+    must agree to rounding.  bfloat16 is held to a loose bound only: in a model this small one token whose branch output lies
+    near zero before a norm can move a logit by a tenth through rounding alone, while a wrong key, mask or state moves it by
+    its whole size."""
+    import random
+    from aien_sovereign_core_mv_b200 import write_random_model
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    d = write_random_model(os.path.join(str(tmp_path), "m"), cfg, 2000 + seed)
+    c, tensors = load_plain(d)
+    draw = np.random.default_rng(seed)
+    reqs = {i + 1: [int(x) for x in draw.integers(0, cfg["vocab"], n)] for i, n in enumerate([rng.randint(1, 30), rng.randint(60, 120), rng.randint(100, 150)])}
+    want = {r: pb.forward(c, tensors, t) for r, t in reqs.items()}
+
+    def steps(mode):
+        if mode == "whole":
+            return [([(rid, t, list(range(len(t))))], [rid]) for rid, t in reqs.items()]
+        out = []
+        if mode == "portions":
+            for rid, t in reqs.items():
+                at = 0
+                while at < len(t):
+                    n = min(rng.choice([1, 2, 3, 7, 16, 33, 64]), len(t) - at)
+                    out.append(([(rid, t[at:at + n], list(range(n)))], [rid] if at + n == len(t) else []))
+                    at += n
+            return out
+        at, live = {r: 0 for r in reqs}, list(reqs)
+        while live:
+            entries, end = [], []
+            for rid in list(live):
+                n = min(len(reqs[rid]) - at[rid], 1 if rng.random() < 0.5 else rng.randint(2, 50))
+                entries.append((rid, reqs[rid][at[rid]:at[rid] + n], list(range(n))))
+                at[rid] += n
+                if at[rid] == len(reqs[rid]):
+                    end.append(rid); live.remove(rid)
+            out.append((entries, end))
+        return out
+
+    for dtype, tol in (("float32", FP32_TOL), ("bfloat16", 0.25)):
+        for mode in ("whole", "portions", "side by side"):
+            eng = H.engine_for(d, dtype, rng.choice([8, 16, 32]), 512, max_requests=4)
+            check(H.run_steps(eng, steps(mode)), want, tol, f"seed {seed} {dtype} {mode}")
+            assert eng.cache_state()["check"] == "" and eng.cache_state()["requests"] == 0
