@@ -103,7 +103,7 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                               const int* __restrict__ token_list, float* __restrict__ part_out, float* __restrict__ part_ml, int* __restrict__ counters,
                               __nv_bfloat16* __restrict__ out, long out_stride,
                               int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int misc_bytes,
-                              FusedQK fq, int kchunk, const float* __restrict__ sinks) {
+                              FusedQK fq, int kchunk, const float* __restrict__ sinks, HeadTerms ht) {
     constexpr int NH = NT * 8;
     extern __shared__ float smem[];
     __shared__ int s_slot[AD_CHUNK];
@@ -258,13 +258,17 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
             }
         }
         // S[nt][e]: key g, head nt*8+2c+e;  S[nt][2+e]: key g+8, same head
+        // terms per head (see HeadTerms): a factor on the scaled score, and slope * (position - key) taken off it
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int h = nt * 8 + 2 * c + e;
-                Sc[(warp * 16 + g) * NH + h] = ok0 ? S[nt][e] * scale : -INFINITY;
-                Sc[(warp * 16 + g + 8) * NH + h] = ok1 ? S[nt][2 + e] * scale : -INFINITY;
+                const int hq = kvh * G + (h < G ? h : 0);
+                const float sc_h = ht.head_scale != nullptr ? scale * ht.head_scale[hq] : scale;
+                const float sl_h = ht.slopes != nullptr ? ht.slopes[hq] : 0.f;
+                Sc[(warp * 16 + g) * NH + h] = ok0 ? S[nt][e] * sc_h - sl_h * (float)(pos - kj0) : -INFINITY;
+                Sc[(warp * 16 + g + 8) * NH + h] = ok1 ? S[nt][2 + e] * sc_h - sl_h * (float)(pos - kj1) : -INFINITY;
             }
     }
     __syncthreads();
@@ -339,12 +343,13 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
     __threadfence();
     const int part_lo = kchunk > 0 ? 0 : s_lo;                      // index of the first block's partial results
     const float* hs = sinks != nullptr ? sinks + kvh * G : nullptr;
+    const float* hg = ht.gate != nullptr ? ht.gate + (size_t)t * ht.ldg + kvh * G : nullptr;
     if (hd <= 128)
         ad_merge_chunks<NH, 1>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
-                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs);
+                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs, hg);
     else
         ad_merge_chunks<NH, 2>(smem, part_out, part_ml, out + (size_t)t * out_stride + (size_t)kvh * G * hd, (size_t)zt * nq + kvh * G,
-                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs);
+                               G, hd, max_splits, part_lo, s_hi - s_lo + 1, threadIdx.x, AD_WARPS * 32, [] { __syncthreads(); }, hs, hg);
 }
 
 template <int HS, int NT>
@@ -352,7 +357,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
                          const int* seq_of_token, const int* positions, const int* token_list, float* part_out, float* part_ml, int* counters,
                          void* out, long out_stride,
                          int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-                         const FusedQK& fq, int kchunk, const float* sinks, cudaStream_t stream) {
+                         const FusedQK& fq, int kchunk, const float* sinks, const HeadTerms& ht, cudaStream_t stream) {
     const int NH = NT * 8;
     size_t loop_bytes = ((size_t)AD_CHUNK * NH + 2 * NH) * 4 + (size_t)NH * AD_CHUNK * 2;          // scores, max/denominator, probabilities
     if (fq.k != nullptr) loop_bytes += (size_t)AD_WARPS * 256 * 4 + (size_t)NH * hd * 2 + 16;      // fused q/k scratch, q
@@ -378,7 +383,7 @@ static int launch_decode(const void* q, long q_stride, const void* kc, const voi
     kern<<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kc,
                  (const __nv_bfloat16*)vc, bt, max_blocks, seq_of_token, positions, token_list,
                  part_out, part_ml, counters, (__nv_bfloat16*)out, out_stride, nq, nkv, hd, page_size, window, scale, max_splits,
-                 misc_bytes, fq, kchunk, sinks);
+                 misc_bytes, fq, kchunk, sinks, ht);
     return launch_status();
 }
 
@@ -394,7 +399,7 @@ static int decode_dispatch(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-    const FusedQK& fq, cudaStream_t stream, int kchunk = 0, const float* sinks = nullptr);
+    const FusedQK& fq, cudaStream_t stream, int kchunk = 0, const float* sinks = nullptr, const HeadTerms& ht = HeadTerms{});
 
 // The same under a chunk mask (kchunk > 0: a token sees only the keys of its own chunk of that many positions) and
 // with per-head softmax sinks (float32 [nq], may be null).  With kchunk > 0, max_splits counts the key blocks a
@@ -409,6 +414,20 @@ AIEN_API int aien_paged_attention_decode_masked(
     return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, token_list, out,
                            out_stride, part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, none, stream,
                            kchunk, sinks);
+}
+
+// The plain split-key kernel with terms per query head (see HeadTerms; each pointer may be null): head_scale and
+// slopes are float32 [nq], gate float32 rows of the step's tokens with ldg numbers between rows.
+AIEN_API int aien_paged_attention_decode_terms(
+    const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+    const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
+    float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
+    const float* head_scale, const float* slopes, const float* gate, long ldg, cudaStream_t stream) {
+    FusedQK none = {};
+    const HeadTerms ht{head_scale, slopes, gate, ldg};
+    return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, token_list, out,
+                           out_stride, part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, none, stream,
+                           0, nullptr, ht);
 }
 
 AIEN_API int aien_paged_attention_decode(
@@ -439,7 +458,7 @@ static int decode_dispatch(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-    const FusedQK& fq, cudaStream_t stream, int kchunk, const float* sinks) {
+    const FusedQK& fq, cudaStream_t stream, int kchunk, const float* sinks, const HeadTerms& ht) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 256 || (hd & 15) || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_splits <= 0) return AIEN_E_SHAPE;
     const int G = nq / nkv;
@@ -451,7 +470,7 @@ static int decode_dispatch(
     if (HS == hs && NT == nt)                                                                                        \
         rc = launch_decode<hs, nt>(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions,  \
                                    token_list, part_out, part_ml, counters, out, out_stride, nq, nkv, hd, page_size, window, scale,        \
-                                   max_splits, T, fq, kchunk, sinks, stream);
+                                   max_splits, T, fq, kchunk, sinks, ht, stream);
     AD_CASE(1, 1) AD_CASE(2, 1) AD_CASE(3, 1) AD_CASE(4, 1) AD_CASE(5, 1) AD_CASE(6, 1) AD_CASE(7, 1) AD_CASE(8, 1)
     AD_CASE(1, 2) AD_CASE(2, 2) AD_CASE(3, 2) AD_CASE(4, 2) AD_CASE(5, 2) AD_CASE(6, 2) AD_CASE(7, 2) AD_CASE(8, 2)
 #undef AD_CASE

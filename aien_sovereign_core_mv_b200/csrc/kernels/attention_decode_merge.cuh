@@ -34,8 +34,10 @@ template <int NH, int PER, typename Sync>
 __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __restrict__ part_out, const float* __restrict__ part_ml,
                                                 __nv_bfloat16* __restrict__ out_row, size_t row0, int G, int hd, int max_splits,
                                                 int s_lo, int nsp, int tid, int nthreads, Sync sync,
-                                                const float* __restrict__ sinks = nullptr) {
-    float* Fi = scratch;                                 // [G]: 1 / total denominator
+                                                const float* __restrict__ sinks = nullptr,
+                                                const float* __restrict__ gate = nullptr) {
+    // gate (when given): float32 [G], the heads' outputs are multiplied by sigmoid(gate[h])
+    float* Fi = scratch;                                 // [G]: 1 / total denominator (times the head's gate)
     float* Fm = Fi + ad_merge_round4((size_t)G);         // [nsp][G]: chunk max, then the chunk's weight
     float* Fl = Fm + ad_merge_round4((size_t)max_splits * G);   // [nsp][G]: chunk denominator; later [AD_MERGE_WAYS][hd]: the series' sums
     float* Ps = Fl;
@@ -66,7 +68,7 @@ __device__ __forceinline__ void ad_merge_chunks(float* scratch, const float* __r
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
         if (sink != -INFINITY) L += expf(sink - M);
-        if (lane == 0) Fi[h] = L > 0.f ? 1.0f / L : 0.f;
+        if (lane == 0) Fi[h] = (L > 0.f ? 1.0f / L : 0.f) * (gate != nullptr ? 1.0f / (1.0f + expf(-__ldcg(gate + h))) : 1.0f);
     }
     sync();                                              // the denominators are used up: their place takes the series' sums
     const int hd4 = hd >> 2;                             // float4 per chunk and head: lane takes lane (and lane + 32)

@@ -95,7 +95,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, int num_tiles, __nv_bfloat16* __restrict__ out, long out_stride,
                   int nq, int nkv, int page_size, int window, float scale_log2e, int cache_rows, int heads_per_cta, int big_boxes,
-                  int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml, int chunk, const float* __restrict__ sinks) {
+                  int nsplit, float* __restrict__ part_o, float* __restrict__ part_ml, int chunk, const float* __restrict__ sinks, HeadTerms ht) {
     using S = PtShape<HD>;
     extern __shared__ uint8_t pt_smem[];
     const uint32_t base = (smem_u32(pt_smem) + 1023u) & ~1023u;
@@ -324,6 +324,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         // maximum only when that has grown by more than 8 (a factor 256, harmless in float32 and
         // in bfloat16's exponent), so the output in tensor memory is rescaled rarely.
         float m_ref = -INFINITY, l_run = 0.f;
+        // terms per head: the score in log2 units becomes s * (scale * head_scale[h]) - slope[h] * (hi - key), made
+        // in place before the limits of the row are applied; the maximum and the exponentials then take it as it is
+        const bool terms = ht.head_scale != nullptr || ht.slopes != nullptr;
+        const float hs_l2 = scale_log2e * (ht.head_scale != nullptr ? ht.head_scale[head_a + h] : 1.0f);
+        const float slope_l2 = ht.slopes != nullptr ? ht.slopes[head_a + h] * 1.4426950408889634f : 0.f;
+        const float sl = terms ? 1.0f : scale_log2e;
 
         for (int j = 0; j < nb; ++j) {
             const int key_base = (kb_begin + j) * PT_BN;
@@ -335,6 +341,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
             for (int c0 = 0; c0 < PT_BN; c0 += 32) tmem_ld32(tS + c0, v + c0);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (terms) {
+                const float at0 = -slope_l2 * (float)(hi - key_base);            // the bias of the block's first key
+#pragma unroll
+                for (int i = 0; i < PT_BN; ++i) v[i] = __float_as_uint(fmaf(__uint_as_float(v[i]), hs_l2, fmaf((float)i, slope_l2, at0)));
+            }
             if (key_base + PT_BN - 1 > hi) {                                     // the block on the diagonal: columns beyond hi
                 const int last = hi - key_base;
 #pragma unroll
@@ -354,7 +365,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int c = 0; c < 4; ++c) mx4[c] = max3(mx4[c], __uint_as_float(v[i + 2 * c]), __uint_as_float(v[i + 2 * c + 1]));
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= scale_log2e;
+            mx *= sl;
             if (j == 0) {
                 m_ref = mx;
             } else {
@@ -392,8 +403,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i]), scale_log2e, neg_base));      // exp2(-inf) = 0 for masked keys
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i + 1]), scale_log2e, neg_base));
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i]), sl, neg_base));      // exp2(-inf) = 0 for masked keys
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(v[c0 + 2 * i + 1]), sl, neg_base));
                     sum += p0 + p1;
                     __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);
                     pk[i] = *reinterpret_cast<uint32_t*>(&pp);
@@ -433,7 +444,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         } else {
         // a sink joins the denominator once, against the same reference as the sums (log2 units); no key, no value
         if (sinks != nullptr && m_ref != -INFINITY) l_run += ex2_approx(sinks[head_a + h] * 1.4426950408889634f - m_ref);
-        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        if (ht.gate != nullptr && r < rows) inv *= 1.0f / (1.0f + expf(-__ldcg(ht.gate + (size_t)(qs + q0 + r) * ht.ldg + head_a + h)));
         __nv_bfloat16* dst = out + (size_t)(qs + q0 + (r < rows ? r : 0)) * out_stride + (size_t)(head_a + h) * HD;
 #pragma unroll 1
         for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -529,9 +541,10 @@ static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMa
                              const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles,
                              void* out, long out_stride, int nq, int nkv, int page_size, int window, float scale, int cache_rows,
                              void* scratch, long scratch_bytes, int max_ctx, int force_splits, int chunk, const float* sinks,
-                             cudaStream_t stream) {
+                             const HeadTerms& ht, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<HD>;
-    if (chunk > 0 || sinks != nullptr) {           // a chunk bounds the keys of a tile, and the merge of key ranges knows no sink
+    // a chunk bounds the keys of a tile, and the merge of key ranges knows neither a sink nor a gate
+    if (chunk > 0 || sinks != nullptr || ht.head_scale != nullptr || ht.slopes != nullptr || ht.gate != nullptr) {
         if (force_splits > 1) return AIEN_E_SHAPE;
         scratch = nullptr;
         scratch_bytes = 0;
@@ -580,7 +593,7 @@ static int launch_prefill_tc(const CUtensorMap& mq, const PtMaps& mk, const PtMa
     float* part_ml = nsplit > 1 ? part_o + part_rows * nsplit * HD : nullptr;
     launch_chain(kern, dim3((unsigned)ctas), dim3(PT_THREADS), (size_t)PtShape<HD>::SMEM, stream, mq, mk, mv, bt, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                                                                      (__nv_bfloat16*)out, out_stride, nq, nkv, page_size, window,
-                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes, nsplit, part_o, part_ml, chunk, sinks);
+                                                                     scale * 1.4426950408889634f, cache_rows, heads_per_cta, big_boxes, nsplit, part_o, part_ml, chunk, sinks, ht);
     if (launch_status() != 0) return launch_status();
     if (nsplit > 1)
         launch_chain(prefill_merge_splits_kernel<HD>, dim3((unsigned)(part_rows / 8)), dim3(256), (size_t)0, stream, (const float*)part_o, (const float*)part_ml,
@@ -605,11 +618,14 @@ AIEN_API int aien_paged_attention_prefill_tc_supports(int hd, int page_size) {
 // force_splits: 0 lets the launch choose, n > 0 asks for n ranges (refused if the scratch is too small).
 // chunk > 0: a query sees only the keys of its own chunk of that many positions; sinks (float32 [nq], may be null):
 // one more term exp(sink) in every head's softmax denominator.  With either, every tile's keys stay in one range.
-AIEN_API int aien_paged_attention_prefill_tc_masked(
+// head_scale, slopes (float32 [nq]) and gate (float32 [tokens of the step, ldg]), each of which may be null: see HeadTerms.
+AIEN_API int aien_paged_attention_prefill_tc_terms(
     const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
     long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
-    int force_splits, int chunk, const float* sinks, cudaStream_t stream) {
+    int force_splits, int chunk, const float* sinks, const float* head_scale, const float* slopes, const float* gate, long ldg,
+    cudaStream_t stream) {
+    const HeadTerms ht{head_scale, slopes, gate, ldg};
     if (num_tiles <= 0) return 0;
     if (chunk < 0) return AIEN_E_SHAPE;
     if (!aien_paged_attention_prefill_tc_supports(hd, page_size) || nkv <= 0 || nq % nkv != 0 || q_rows <= 0 || cache_rows <= 0)
@@ -638,9 +654,19 @@ AIEN_API int aien_paged_attention_prefill_tc_masked(
     if (!big_boxes) { mk.blk = mk.m[0]; mv.blk = mv.m[0]; }
     if (hd == 64)
         return launch_prefill_tc<64>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                     nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, stream);
+                                     nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, ht, stream);
     return launch_prefill_tc<128>(mq, mk, mv, big_boxes, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles, out, out_stride,
-                                  nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, stream);
+                                  nq, nkv, page_size, window, scale, cache_rows, scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, ht, stream);
+}
+
+AIEN_API int aien_paged_attention_prefill_tc_masked(
+    const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
+    int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
+    long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
+    int force_splits, int chunk, const float* sinks, cudaStream_t stream) {
+    return aien_paged_attention_prefill_tc_terms(q, q_stride, q_rows, k_cache, v_cache, cache_rows, block_table, max_blocks, q_start, ctx_len,
+                                                 tile_seq, tile_q0, num_tiles, out, out_stride, nq, nkv, hd, page_size, window, scale,
+                                                 scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, nullptr, nullptr, nullptr, 0, stream);
 }
 
 AIEN_API int aien_paged_attention_prefill_tc_split(

@@ -21,6 +21,16 @@
 
 #define AIEN_API extern "C" __attribute__((visibility("default")))
 
+// Terms per query head that an attention kernel may be given beside the scaled score q.k * scale (any may be null):
+// head_scale[h] multiplies it; slopes[h] * (query position - key position) is taken off it; the head's output is
+// multiplied by sigmoid(gate[t * ldg + h]) (float32 rows of the step's tokens).
+struct HeadTerms {
+    const float* head_scale;
+    const float* slopes;
+    const float* gate;
+    long ldg;
+};
+
 namespace aien {
 
 __device__ __forceinline__ float to_f(float v) { return v; }

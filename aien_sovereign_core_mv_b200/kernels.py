@@ -154,6 +154,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_prefill_tc_masked": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_masked": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, I, P, P],
+        "aien_paged_attention_decode_terms": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P, P, P, L, P],
+        "aien_paged_attention_prefill_tc_terms": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P, P, P, L, P],
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
@@ -912,15 +914,17 @@ def decode_stream_supports(num_q_heads: int, num_kv_heads: int, head_dim: int, p
 def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, out,
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
                            max_splits, token_list=None, num_tokens=None, impl: Optional[str] = None, chunk: int = 0,
-                           sinks: Optional[torch.Tensor] = None) -> None:
+                           sinks: Optional[torch.Tensor] = None, head_scale: Optional[torch.Tensor] = None,
+                           slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
     counters are one small device buffer that every launch finds zero and leaves zero.
     ``impl``: "stream" (TMA ring, persistent CTAs; where the sizes allow) or "direct" (one CTA per
     chunk); both give the same bits.  Default from ``AIEN_B200_DECODE_ATTENTION``, else "stream".
     ``chunk`` > 0 (a token sees only the keys of its own chunk of that many positions; ``max_splits`` then counts
-    the 128-key blocks a chunk can touch, see decode_splits) and ``sinks`` (float32 [heads]) are the direct kernel's."""
+    the 128-key blocks a chunk can touch, see decode_splits) and ``sinks`` (float32 [heads]) are the direct kernel's,
+    and so are the terms per head ``head_scale``, ``slopes`` and ``gate`` (see :func:`paged_attention_generic`)."""
     global _ticket_counters
-    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml, sinks)
+    _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml, sinks, head_scale, slopes, gate)
     # seq_of_token None: token t belongs to row t of the block table.  token_list: serve only these tokens.
     T = q.shape[0] if token_list is None else int(num_tokens)
     if _ticket_counters is None:
@@ -931,6 +935,15 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
     assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
     impl = impl or _DECODE_ATTN_IMPL
+    if head_scale is not None or slopes is not None or gate is not None:
+        assert not chunk and sinks is None
+        _check_head_terms(num_q_heads, head_scale, slopes, gate)
+        _check(lib().aien_paged_attention_decode_terms(
+            _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
+            _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
+            page_size, window, float(scale), max_splits, T, _p(head_scale), _p(slopes), _p(gate),
+            gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_decode_terms")
+        return
     if chunk or sinks is not None:
         assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
         _check(lib().aien_paged_attention_decode_masked(
@@ -948,6 +961,12 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
         page_size, window, float(scale), max_splits, T, _stream()), "paged_attention_decode")
+
+
+def _check_head_terms(num_q_heads: int, head_scale, slopes, gate) -> None:
+    for v in (head_scale, slopes):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == num_q_heads)
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] >= num_q_heads)
 
 
 def attention_decode_stream_error() -> int:
@@ -1133,7 +1152,8 @@ def prefill_split_scratch_bytes(num_tiles: int, num_q_heads: int, head_dim: int,
 def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_start, ctx_len, tile_seq, tile_q0, num_tiles,
                             out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None,
                             scratch: Optional[torch.Tensor] = None, max_ctx: int = 0, splits: int = 0, chunk: int = 0,
-                            sinks: Optional[torch.Tensor] = None) -> None:
+                            sinks: Optional[torch.Tensor] = None, head_scale: Optional[torch.Tensor] = None,
+                            slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
     cores).  ``tile_seq``/``tile_q0``: for every 128-token query tile, the index of its request in
     the step and the tile's offset inside that request's portion.  ``impl``: "tc" (tcgen05, where
@@ -1142,8 +1162,12 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
     tcgen05 kernel cut the keys of a step with few tiles into ranges that run on separate SMs;
     ``splits`` > 0 asks for that many ranges (tests).  ``chunk`` > 0 (a query sees only the keys of
     its own chunk of that many positions) and ``sinks`` (float32 [heads], one more term exp(sink) in
-    the softmax denominator): both kernels take them; the tcgen05 kernel then keeps every tile's keys in one range."""
-    _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out, sinks)
+    the softmax denominator): both kernels take them; the tcgen05 kernel then keeps every tile's keys in one range.
+    ``head_scale``, ``slopes``, ``gate`` (see :func:`paged_attention_generic`): the tcgen05 kernel's alone; it keeps
+    every tile's keys in one range with these too."""
+    _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out, sinks, head_scale, slopes, gate)
+    terms = head_scale is not None or slopes is not None or gate is not None
+    _check_head_terms(num_q_heads, head_scale, slopes, gate)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -1154,13 +1178,16 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
         if scratch is not None:
             _dev(scratch)
             assert scratch.dtype == torch.float32 and scratch.is_contiguous()
-        _check(lib().aien_paged_attention_prefill_tc_masked(
+        _check(lib().aien_paged_attention_prefill_tc_terms(
             _p(q), q.stride(0), q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0], _p(block_table), max_blocks, _p(q_start),
             _p(ctx_len), _p(tile_seq), _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim,
             page_size, window, float(scale), _p(scratch) if scratch is not None else None,
-            scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), int(chunk), _p(sinks), _stream()),
+            scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), int(chunk), _p(sinks),
+            _p(head_scale), _p(slopes), _p(gate), gate.stride(0) if gate is not None else 0, _stream()),
             "paged_attention_prefill_tc")
         return
+    if terms:
+        raise KernelError("paged_attention_prefill: only the tcgen05 kernel takes terms per head")
     _check(lib().aien_paged_attention_prefill(
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(q_start), _p(ctx_len), _p(tile_seq),
         _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window,
@@ -1616,8 +1643,9 @@ def grouped_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Ten
 
 # ---------------------------------------------------------------------------- attention with a distance bias
 def biased_attention_workspace_bytes(lim, num_heads: int, value_dim: int, window: int) -> int:
-    """Scratch of :func:`biased_attention` for the largest step."""
-    return 4096
+    """Scratch of :func:`biased_attention` for the largest step: the partial results of the split-key kernel."""
+    splits = (lim.max_context + DECODE_CHUNK - 1) // DECODE_CHUNK
+    return lim.max_seqs * num_heads * splits * (value_dim + 2) * 4 + 4096
 
 
 def biased_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor, num_q_heads: int,
@@ -1625,9 +1653,39 @@ def biased_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
                      slopes: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> None:
     """Attention of the step's tokens over one cache group with, per head, a factor on the scaled score, a bias
     -slope * (query position - key position) and a sigmoid gate on the output; an optional window; values of size
-    ``value_dim``.  Picks the kernel for the step."""
+    ``value_dim``.  Picks the kernel for the step: in bfloat16 with values as large as keys, portions of prompts go
+    through the tcgen05 kernel and tokens that come alone through the split-key kernel; all else through the plain one."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    terms = dict(head_scale=head_scale, slopes=slopes, gate=gate)
+    fast = (_FORCE_ATTN != "generic" and value_dim == head_dim and out.dtype == torch.bfloat16
+            and decode_attention_supports(q, k2, num_q_heads, num_kv_heads, head_dim))
+
+    def single_tokens(tokens, n):
+        splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+        part_out = ctx.workspace.take((n * num_q_heads * splits * head_dim,), torch.float32)
+        part_ml = ctx.workspace.take((n * num_q_heads * splits * 2,), torch.float32)
+        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, None if tokens is None else ctx.seq_of_token,
+                               ctx.positions, out, part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                               splits, token_list=tokens, num_tokens=n, impl="direct", **terms)
+
+    splits_ok = fast and decode_masked_takes(num_q_heads, num_kv_heads, head_dim, max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK))
+    if ctx.decode_only and splits_ok:
+        single_tokens(None, q.shape[0])
+        return
+    if (not ctx.decode_only and fast and ctx.prefill_tiles is not None and _PREFILL_IMPL == "tc"
+            and prefill_tc_supports(q, out, head_dim, group.page_size)):
+        tile_seq, tile_q0, n = ctx.prefill_tiles
+        if n > 0:
+            paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, impl="tc", **terms)
+        tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
+        if nd > 0 and splits_ok:
+            single_tokens(tokens, nd)
+        elif nd > 0:
+            paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                                    num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim,
+                                    token_list=tokens, num_tokens=nd, **terms)
+        return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
-                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim,
-                            head_scale=head_scale, slopes=slopes, gate=gate)
+                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim, **terms)

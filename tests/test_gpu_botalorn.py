@@ -213,10 +213,11 @@ def test_token_shift_across_portions_single_tokens_and_slots(dtype):
     H.assert_close(state[2].cpu().numpy(), f64(hn[0][-1]), 2e-6, "the slot holds the last row as it was before the shift")
 
 
-def _paged(tables, page, rows_k, rows_v, dtype, slots=64):
-    """Caches [slots * page, ...] whose pages lie in the scrambled order of ``tables``; rows_*[s] are request s's rows by position."""
-    k = torch.full((slots * page,) + tuple(rows_k[0].shape[1:]), float("nan"), dtype=dtype)
-    v = torch.full((slots * page,) + tuple(rows_v[0].shape[1:]), float("nan"), dtype=dtype)
+def _paged(tables, page, rows_k, rows_v, dtype, slots=64, fill=float("nan")):
+    """Caches [slots * page, ...] whose pages lie in the scrambled order of ``tables``; rows_*[s] are request s's rows by
+    position; every other row holds ``fill``."""
+    k = torch.full((slots * page,) + tuple(rows_k[0].shape[1:]), fill, dtype=dtype)
+    v = torch.full((slots * page,) + tuple(rows_v[0].shape[1:]), fill, dtype=dtype)
     for s, tab in enumerate(tables):
         for p in range(rows_k[s].shape[0]):
             at = tab[p // page] * page + p % page
@@ -280,6 +281,74 @@ def test_biased_attention_at_the_edges_of_its_window(dtype, window, page, heads,
     run([(0, 60, 70), (1, 40, 1)])                                 # a portion in the middle beside a single token
     run([(0, 149, 1), (1, 17, 1)])                                 # single tokens (decoding)
     run([(1, 7, 2), (0, 127, 3)])                                  # two tokens before a page border, three across one
+
+
+@pytest.mark.parametrize("window,page,heads,kv,dim", [(130, 16, 8, 2, 64), (0, 16, 4, 4, 128), (64, 32, 16, 2, 128), (257, 8, 6, 1, 64), (1, 16, 2, 2, 64)])
+def test_biased_attention_through_the_tensor_core_kernels(window, page, heads, kv, dim):
+    """The same construction as above (the oldest visible key takes nearly all the weight) in bfloat16 with heads of 64
+    and 128, where portions of prompts go through the tcgen05 kernel and single tokens through the split-key kernel:
+    windows that end inside a block of 128 keys, keys hundreds of positions back, several query tiles, a request that
+    continues beside one that starts, and portions beside single tokens in one step."""
+    from types import SimpleNamespace
+    from aien_sovereign_core_mv_b200 import kernels as K
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(window * 11 + dim + heads)
+    lens = [420, 141]
+    scale = dim ** -0.5
+    temp = (torch.rand(heads, generator=g) + 0.75)
+    slope = torch.tensor(pb.slopes(heads), dtype=torch.float32)
+    u = torch.randn(kv, dim, generator=g)
+    u = u / u.norm(dim=-1, keepdim=True)
+    ks, vs, qs = [], [], []
+    for n in lens:
+        grow = (3.0 + float(slope.max())) / (scale * 0.75)
+        amp = (n - torch.arange(n, dtype=torch.float32)) * grow / 4.0
+        ks.append((u[None] * amp[:, None, None] / 4.0 + 0.05 * torch.randn(n, kv, dim, generator=g)).to(dtype).float())
+        vs.append(torch.randn(n, kv, dim, generator=g).to(dtype).float())
+        qs.append((u.repeat_interleave(heads // kv, 0)[None] * 16.0 + 0.05 * torch.randn(n, heads, dim, generator=g)).to(dtype).float())
+    order = [int(i) for i in torch.randperm(96, generator=g)]
+    n0 = (lens[0] + page - 1) // page
+    tables = [order[:n0], order[n0:n0 + (lens[1] + page - 1) // page]]
+    # The tensor-core kernels fetch whole blocks of rows and give the rows no query may see the weight zero, so the rows
+    # of a pool must be finite (the engine's pools start as zeros); here they are large, so that any weight on them shows.
+    kc, vc, bt, width = _paged(tables, page, ks, vs, dtype, slots=96, fill=3000.0)
+    gate = torch.randn(sum(lens), heads + 3, generator=g)
+    def run(entries):
+        pos, sot, rows, gr, q_start, ctx_len = [], [], [], [], [0], []
+        for i, (s, p0, n) in enumerate(entries):
+            pos += list(range(p0, p0 + n)); sot += [i] * n
+            rows.append(qs[s][p0:p0 + n].reshape(n, heads * dim))
+            gr.append(gate[sum(lens[:s]) + p0: sum(lens[:s]) + p0 + n])
+            q_start.append(q_start[-1] + n); ctx_len.append(p0 + n)
+        ctx = make_ctx(dtype, pos, sot, q_start, ctx_len)
+        if not ctx.decode_only:                                    # as the engine lays a mixed step out
+            ts, tq, single = [], [], []
+            for i, (_, _, n) in enumerate(entries):
+                if n == 1:
+                    single.append(q_start[i])
+                    continue
+                ts += [i] * ((n + 127) // 128); tq += list(range(0, n, 128))
+            ctx.prefill_tiles = (i32(ts or [0]), i32(tq or [0]), len(ts))
+            ctx.single_tokens = (i32(single or [0]), len(single))
+        q = torch.cat(rows).to(dtype).cuda()
+        out = torch.zeros(len(pos), heads * dim, dtype=dtype).cuda()
+        group = SimpleNamespace(block_table=torch.stack([bt[s] for s, _, _ in entries]).contiguous(), max_blocks=width, page_size=page)
+        K.biased_attention(ctx, q, kc, vc, group, out, heads, kv, dim, dim, window, scale, temp.cuda(), slope.cuda(),
+                           torch.cat(gr).contiguous().cuda())
+        torch.cuda.synchronize()
+        assert K.attention_prefill_tc_error() == 0
+        want = []
+        for (s, p0, n), g_ in zip(entries, gr):
+            allpos = list(range(lens[s]))
+            o = pb.biased_window_attention(f64(qs[s][p0:p0 + n]), f64(ks[s]), f64(vs[s]), allpos[p0:p0 + n], allpos, scale, f64(temp), window, f64(slope))
+            want.append(o * pb.sigmoid(f64(g_[:, :heads]))[:, :, None])
+        H.assert_close(out.float().cpu().numpy().reshape(len(pos), heads, dim), np.concatenate(want), 1.5e-2, f"window {window}, entries {entries}")
+
+    run([(0, 0, 420), (1, 0, 141)])                                # whole prompts: four query tiles and two
+    run([(0, 250, 170), (1, 140, 1)])                              # a portion that continues (and ends inside a block of keys) beside a single token
+    run([(0, 419, 1), (1, 17, 1)])                                 # single tokens (decoding), one far along
+    run([(1, 127, 2), (0, 383, 3), (1, 5, 1), (0, 2, 2)])          # two tokens across a block's border, three across another, a single token
+    run([(0, 128, 128)])                                           # exactly one tile from a block's border on
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
