@@ -3,11 +3,16 @@
 //     S <- g S ;   u = beta (v - S^T k) ;   S <- S + k u^T ;   o = S^T q
 // (g a decay in (0, 1], beta in (0, 1), k a unit vector; heads/G value heads share one q/k head).  Column j of S
 // never meets another column: S^T k, u, the update and S^T q are all per column.  So a thread owns part of one column
-// in registers and a portion is walked token by token with no barrier inside a chunk of tokens: a warp holds 8
-// columns x 4 row ranges (the four partial dot products meet through two shuffles), a CTA 32 columns of one head of
-// one request.  q, k, v, g and beta of the next chunk of tokens arrive through cp.async while the current one is
-// walked.  Every operation is float32 and runs in the order written above, so a token's output depends on the
-// tokens before it only through S, whatever the cut of the prompt or the batch.
+// in registers and a portion is walked token by token with no barrier inside a chunk of tokens.  Both products are
+// taken from the state as the token finds it, in one pass over the registers:
+//     a = S^T k ,  b = S^T q ,  c = k . q ;   u = beta (v - g a) ;   o = g b + c u ;   S <- g S + k u^T
+// which is the same arithmetic with the decay drawn out of the sums.  A warp holds 32/RS columns x RS row ranges (the
+// partial sums meet through log2(RS) shuffles), a CTA four warps' columns of one head of one request.  What the
+// walk is bound by is the reading of k and q from shared memory, once per token and thread: the row ranges lie
+// DPT + 4 floats apart there, so that the 16-byte reads of a warp fall into different banks.  q, k, v, g and beta of
+// the next chunk of tokens arrive through cp.async while the current one is walked, and the next token's are taken
+// into registers while the current one's sums are on their way.  Every operation is float32 and a token's are the
+// same whatever the cut of the prompt or the batch, so its output depends on the tokens before it only through S.
 //
 // The state lives in the request's slot between steps (a portion whose first token has position 0 starts from zero).
 //
@@ -19,107 +24,170 @@
 namespace aien {
 
 constexpr int DR_THREADS = 128;
-constexpr int DR_COLS = 32;         // columns of S per CTA
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-template <int DPT>
+template <int DPT, int RS>
 struct DeltaCfg {
-    static constexpr int DP = 4 * DPT;                         // rows of S, padded
-    static constexpr int TC = DPT <= 32 ? 16 : 8;              // tokens per chunk
-    static constexpr int ROW = 2 * DP + DR_COLS + 4;           // floats per token: k | q | v | g, beta, -, -
+    static constexpr int DP = RS * DPT;                        // rows of S, padded
+    static constexpr int PS = DPT == 4 ? 4 : DPT + 4;          // floats between two row ranges of k (or q) in shared memory
+    static constexpr int CW = 32 / RS;                         // columns per warp
+    static constexpr int COLS = (DR_THREADS / 32) * CW;        // columns of S per CTA
+    static constexpr int KQ = RS * PS;                         // floats of k (or q) per token, padded
+    static constexpr int ROW = 2 * KQ + COLS + 4;              // floats per token: k | q | v | g, beta, -, -
+    static constexpr int TC = 2 * 16 * ROW * 4 <= 48 * 1024 ? 16 : 8;   // tokens per chunk: two chunks within 48 KB
 };
 
-template <int DPT>
-__device__ __forceinline__ void delta_fetch(float* __restrict__ buf, const float* __restrict__ qkv, long ld, int q_col, int k_col,
-                                            int v_col, const float* __restrict__ gb, long ldgb, int h, int heads, int t, int t1,
-                                            int D, int V, int col0) {
-    using C = DeltaCfg<DPT>;
-    for (int idx = threadIdx.x; idx < C::TC * C::ROW; idx += DR_THREADS) {
-        const int tok = idx / C::ROW, e = idx - tok * C::ROW;
-        const int tt = t + tok;
-        float* dst = buf + idx;
-        const float* src = nullptr;
-        if (tt < t1) {
-            if (e < C::DP) { if (e < D) src = qkv + (size_t)tt * ld + k_col + e; }
-            else if (e < 2 * C::DP) { if (e - C::DP < D) src = qkv + (size_t)tt * ld + q_col + (e - C::DP); }
-            else if (e < 2 * C::DP + DR_COLS) { if (col0 + (e - 2 * C::DP) < V) src = qkv + (size_t)tt * ld + v_col + col0 + (e - 2 * C::DP); }
-            else if (e == 2 * C::DP + DR_COLS) src = gb + (size_t)tt * ldgb + h;
-            else if (e == 2 * C::DP + DR_COLS + 1) src = gb + (size_t)tt * ldgb + heads + h;
-        }
-        if (src != nullptr) cp_async4(dst, src);
-        else *dst = 0.f;
-    }
-    cp_async_commit();
-}
+// What one thread copies for every token of a chunk: up to NE pieces, found once per kernel (where in the token's
+// row of the source, where in its row of shared memory, 16 bytes or 4), so that a chunk's copies are an address
+// and a cp.async each.  The walk shares its warps with the copies, so their instructions count.
+template <int DPT, int RS>
+struct DeltaPieces {
+    using C = DeltaCfg<DPT, RS>;
+    static constexpr int NE = (2 * C::DP + C::COLS + 2 + DR_THREADS - 1) / DR_THREADS;
+    const float* src[NE];
+    long stride[NE];
+    int dst[NE];
+    int kind[NE];                                              // 0: none, 1: 4 bytes, 2: 16 bytes; +4: always zero
 
-template <int DPT>
+    __device__ __forceinline__ void find(bool vec, const float* qkv, long ld, int q_col, int k_col, int v_col, const float* gb,
+                                         long ldgb, int h, int heads, int D, int V, int col0) {
+        const int unit = vec ? 4 : 1;
+        const int n_kq = C::DP / unit, n_v = C::COLS / unit;
+#pragma unroll
+        for (int i = 0; i < NE; ++i) {
+            const int e = threadIdx.x + i * DR_THREADS;
+            src[i] = qkv; stride[i] = ld; dst[i] = 0; kind[i] = 0;
+            if (e < 2 * n_kq) {
+                const int which = e >= n_kq, r = (e - which * n_kq) * unit;        // 0: k, 1: q; row r
+                dst[i] = which * C::KQ + (r / DPT) * C::PS + (r % DPT);
+                src[i] = qkv + (which ? q_col : k_col) + r;
+                kind[i] = (vec ? 2 : 1) + (r < D ? 0 : 4);
+            } else if (e < 2 * n_kq + n_v) {
+                const int c = (e - 2 * n_kq) * unit;
+                dst[i] = 2 * C::KQ + c;
+                src[i] = qkv + v_col + col0 + c;
+                kind[i] = (vec ? 2 : 1) + (col0 + c < V ? 0 : 4);
+            } else if (e < 2 * n_kq + n_v + 2) {
+                const int w = e - 2 * n_kq - n_v;                                   // 0: decay, 1: beta
+                dst[i] = 2 * C::KQ + C::COLS + w;
+                src[i] = gb + w * heads + h;
+                stride[i] = ldgb;
+                kind[i] = 1;
+            }
+        }
+    }
+
+    __device__ __forceinline__ void fetch(float* __restrict__ buf, int t, int t1) const {
+#pragma unroll 4
+        for (int tok = 0; tok < C::TC; ++tok) {
+            const int tt = t + tok;
+#pragma unroll
+            for (int i = 0; i < NE; ++i) {
+                if (kind[i] == 0) continue;
+                float* d = buf + tok * C::ROW + dst[i];
+                const bool wide = (kind[i] & 2) != 0;
+                if (tt < t1 && kind[i] < 4) {
+                    const float* sp = src[i] + (size_t)tt * stride[i];
+                    if (wide) cp_async16(d, sp);
+                    else cp_async4(d, sp);
+                } else if (wide) {
+                    *reinterpret_cast<float4*>(d) = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else {
+                    *d = 0.f;
+                }
+            }
+        }
+        cp_async_commit();
+    }
+};
+
+template <int DPT, int RS>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ qkv, long ld, int q_off, int k_off, int v_off, const float* __restrict__ gb, long ldgb,
                   float* __restrict__ state, size_t state_stride, size_t s_off, const int* __restrict__ slot_map,
                   const int* __restrict__ q_start, const int* __restrict__ positions, float* __restrict__ o, long ldo,
                   int heads, int G, int D, int V) {
-    using C = DeltaCfg<DPT>;
+    using C = DeltaCfg<DPT, RS>;
+    constexpr int N4 = DPT / 4;
     __shared__ __align__(16) float bufs[2][C::TC * C::ROW];
     const int s = blockIdx.z, h = blockIdx.y, kvh = h / (heads / G);
     const int t0 = q_start[s], t1 = q_start[s + 1];
     if (t1 <= t0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int rs = lane >> 3, cw = lane & 7;
-    const int col0 = blockIdx.x * DR_COLS, cl = warp * 8 + cw, col = col0 + cl;
+    const int rs = lane / C::CW, cw = lane % C::CW;
+    const int col0 = blockIdx.x * C::COLS, cl = warp * C::CW + cw, col = col0 + cl;
     const bool col_ok = col < V;
     const int i0 = rs * DPT;
     float* S = state + (size_t)slot_map[s] * state_stride + s_off + (size_t)h * D * V;
     const int q_col = q_off + kvh * D, k_col = k_off + kvh * D, v_col = v_off + h * V;
 
-    delta_fetch<DPT>(bufs[0], qkv, ld, q_col, k_col, v_col, gb, ldgb, h, heads, t0, t1, D, V, col0);
+    // 16-byte copies where every piece of four neighbours starts on a 16-byte boundary and lies inside or outside whole
+    const bool vec = ((reinterpret_cast<uintptr_t>(qkv) & 15) == 0) && ((ld | q_col | k_col | v_col | D | V) & 3) == 0;
+    DeltaPieces<DPT, RS> pieces;
+    pieces.find(vec, qkv, ld, q_col, k_col, v_col, gb, ldgb, h, heads, D, V, col0);
+    pieces.fetch(bufs[0], t0, t1);
     float Sr[DPT];
     const bool fresh = positions[t0] == 0;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) Sr[i] = (!fresh && col_ok && i0 + i < D) ? S[(size_t)(i0 + i) * V + col] : 0.f;
 
+    float4 kc[N4], qc[N4];
+    float vj, g, beta;
+    auto take = [&](const float* row) {                        // one token's numbers into registers
+        const float4* kk = reinterpret_cast<const float4*>(row + rs * C::PS);
+        const float4* qq = reinterpret_cast<const float4*>(row + C::KQ + rs * C::PS);
+#pragma unroll
+        for (int i = 0; i < N4; ++i) { kc[i] = kk[i]; qc[i] = qq[i]; }
+        vj = row[2 * C::KQ + cl];
+        g = row[2 * C::KQ + C::COLS];
+        beta = row[2 * C::KQ + C::COLS + 1];
+    };
+
     int b = 0;
     for (int t = t0; t < t1; t += C::TC, b ^= 1) {
         cp_async_wait_all();
         __syncthreads();                                        // chunk b has arrived; everyone is done with chunk b^1
-        if (t + C::TC < t1) delta_fetch<DPT>(bufs[b ^ 1], qkv, ld, q_col, k_col, v_col, gb, ldgb, h, heads, t + C::TC, t1, D, V, col0);
+        if (t + C::TC < t1) pieces.fetch(bufs[b ^ 1], t + C::TC, t1);
         const int n = t1 - t < C::TC ? t1 - t : C::TC;
+        take(bufs[b]);
         for (int tt = 0; tt < n; ++tt) {
-            const float* row = bufs[b] + tt * C::ROW;
-            const float4* kk = reinterpret_cast<const float4*>(row + i0);
-            const float4* qq = reinterpret_cast<const float4*>(row + C::DP + i0);
-            const float vj = row[2 * C::DP + cl];
-            const float g = row[2 * C::DP + DR_COLS], beta = row[2 * C::DP + DR_COLS + 1];
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float a[4] = {0.f, 0.f, 0.f, 0.f}, bq[4] = {0.f, 0.f, 0.f, 0.f}, c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 k4 = kk[i];
-                Sr[4 * i + 0] *= g; a0 = fmaf(Sr[4 * i + 0], k4.x, a0);
-                Sr[4 * i + 1] *= g; a1 = fmaf(Sr[4 * i + 1], k4.y, a1);
-                Sr[4 * i + 2] *= g; a2 = fmaf(Sr[4 * i + 2], k4.z, a2);
-                Sr[4 * i + 3] *= g; a3 = fmaf(Sr[4 * i + 3], k4.w, a3);
+            for (int i = 0; i < N4; ++i) {
+                const float4 k4 = kc[i], q4 = qc[i];
+                a[0] = fmaf(Sr[4 * i + 0], k4.x, a[0]); bq[0] = fmaf(Sr[4 * i + 0], q4.x, bq[0]); c[0] = fmaf(k4.x, q4.x, c[0]);
+                a[1] = fmaf(Sr[4 * i + 1], k4.y, a[1]); bq[1] = fmaf(Sr[4 * i + 1], q4.y, bq[1]); c[1] = fmaf(k4.y, q4.y, c[1]);
+                a[2] = fmaf(Sr[4 * i + 2], k4.z, a[2]); bq[2] = fmaf(Sr[4 * i + 2], q4.z, bq[2]); c[2] = fmaf(k4.z, q4.z, c[2]);
+                a[3] = fmaf(Sr[4 * i + 3], k4.w, a[3]); bq[3] = fmaf(Sr[4 * i + 3], q4.w, bq[3]); c[3] = fmaf(k4.w, q4.w, c[3]);
             }
-            float sk = (a0 + a1) + (a2 + a3);
-            sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-            sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-            const float u = beta * (vj - sk);
-            a0 = a1 = a2 = a3 = 0.f;
+            float sa = (a[0] + a[1]) + (a[2] + a[3]), sb = (bq[0] + bq[1]) + (bq[2] + bq[3]), sc = (c[0] + c[1]) + (c[2] + c[3]);
 #pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 k4 = kk[i], q4 = qq[i];
-                Sr[4 * i + 0] = fmaf(k4.x, u, Sr[4 * i + 0]); a0 = fmaf(Sr[4 * i + 0], q4.x, a0);
-                Sr[4 * i + 1] = fmaf(k4.y, u, Sr[4 * i + 1]); a1 = fmaf(Sr[4 * i + 1], q4.y, a1);
-                Sr[4 * i + 2] = fmaf(k4.z, u, Sr[4 * i + 2]); a2 = fmaf(Sr[4 * i + 2], q4.z, a2);
-                Sr[4 * i + 3] = fmaf(k4.w, u, Sr[4 * i + 3]); a3 = fmaf(Sr[4 * i + 3], q4.w, a3);
+            for (int off = C::CW; off < 32; off <<= 1) {
+                sa += __shfl_xor_sync(0xffffffffu, sa, off);
+                sb += __shfl_xor_sync(0xffffffffu, sb, off);
+                sc += __shfl_xor_sync(0xffffffffu, sc, off);
             }
-            float oj = (a0 + a1) + (a2 + a3);
-            oj += __shfl_xor_sync(0xffffffffu, oj, 8);
-            oj += __shfl_xor_sync(0xffffffffu, oj, 16);
+            const float gg = g;
+            const float u = beta * (vj - gg * sa);
+            const float oj = fmaf(sc, u, gg * sb);
+#pragma unroll
+            for (int i = 0; i < N4; ++i) {
+                Sr[4 * i + 0] = fmaf(kc[i].x, u, gg * Sr[4 * i + 0]);
+                Sr[4 * i + 1] = fmaf(kc[i].y, u, gg * Sr[4 * i + 1]);
+                Sr[4 * i + 2] = fmaf(kc[i].z, u, gg * Sr[4 * i + 2]);
+                Sr[4 * i + 3] = fmaf(kc[i].w, u, gg * Sr[4 * i + 3]);
+            }
+            if (tt + 1 < n) take(bufs[b] + (tt + 1) * C::ROW);  // the next token's, while this one's output leaves
             if (rs == 0 && col_ok) o[(size_t)(t + tt) * ldo + (size_t)h * V + col] = oj;
         }
     }
@@ -159,12 +227,14 @@ grouped_gated_rmsnorm_kernel(const float* __restrict__ o, long ldo, const TP* __
 
 using namespace aien;
 
-template <int DPT>
-static void launch_delta_rule(dim3 grid, cudaStream_t stream, const float* qkv, long ld, int q_off, int k_off, int v_off, const float* gb,
+template <int DPT, int RS>
+static void launch_delta_rule(cudaStream_t stream, const float* qkv, long ld, int q_off, int k_off, int v_off, const float* gb,
                               long ldgb, float* state, size_t state_stride, size_t s_off, const int* slot_map, const int* q_start,
-                              const int* positions, float* o, long ldo, int heads, int G, int D, int V) {
-    delta_rule_kernel<DPT><<<grid, DR_THREADS, 0, stream>>>(qkv, ld, q_off, k_off, v_off, gb, ldgb, state, state_stride, s_off, slot_map,
-                                                            q_start, positions, o, ldo, heads, G, D, V);
+                              const int* positions, float* o, long ldo, int S, int heads, int G, int D, int V) {
+    constexpr int COLS = DeltaCfg<DPT, RS>::COLS;
+    dim3 grid((V + COLS - 1) / COLS, heads, S);
+    delta_rule_kernel<DPT, RS><<<grid, DR_THREADS, 0, stream>>>(qkv, ld, q_off, k_off, v_off, gb, ldgb, state, state_stride, s_off,
+                                                                slot_map, q_start, positions, o, ldo, heads, G, D, V);
 }
 
 // qkv float32 [T, ld]: prepared q (G*D) at q_off, k (G*D) at k_off, v (heads*V) at v_off; gb float32 [T, ldgb]: decay
@@ -175,16 +245,14 @@ AIEN_API int aien_delta_rule(const float* qkv, long ld, int q_off, int k_off, in
                              float* o, long ldo, int S, int heads, int G, int D, int V, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (heads <= 0 || G <= 0 || heads % G || D <= 0 || D > 256 || V <= 0 || S > 65535 || heads > 65535) return AIEN_E_SHAPE;
-    dim3 grid((V + DR_COLS - 1) / DR_COLS, heads, S);
-    const int dpt = (D + 3) / 4;
-#define DR_CASE(N) launch_delta_rule<N>(grid, stream, qkv, ld, q_off, k_off, v_off, gb, ldgb, state, state_stride, s_off, slot_map, q_start, positions, o, ldo, heads, G, D, V)
-    if (dpt <= 4) DR_CASE(4);
-    else if (dpt <= 8) DR_CASE(8);
-    else if (dpt <= 16) DR_CASE(16);
-    else if (dpt <= 24) DR_CASE(24);
-    else if (dpt <= 32) DR_CASE(32);
-    else if (dpt <= 48) DR_CASE(48);
-    else DR_CASE(64);
+#define DR_CASE(N, R) launch_delta_rule<N, R>(stream, qkv, ld, q_off, k_off, v_off, gb, ldgb, state, state_stride, s_off, slot_map, q_start, positions, o, ldo, S, heads, G, D, V)
+    if (D <= 16) DR_CASE(4, 4);
+    else if (D <= 32) DR_CASE(8, 4);
+    else if (D <= 64) DR_CASE(8, 8);
+    else if (D <= 96) DR_CASE(12, 8);
+    else if (D <= 128) DR_CASE(16, 8);
+    else if (D <= 192) DR_CASE(24, 8);
+    else DR_CASE(32, 8);
 #undef DR_CASE
     return launch_status();
 }

@@ -48,8 +48,9 @@ __global__ void replicate_streams_kernel(float* __restrict__ x, size_t per, int 
 // pstride apart; prev: the pack whose mix/out apply to it.  cur: the pack whose in[] forms u.  h: the normed row.
 // shift_w (or null): the fused token shift of a step of single tokens, with the float32 slots `shift_state`
 // [slots][H], slot_map[t] and positions[t].
-template <typename TA, typename TH>
-__global__ void __launch_bounds__(256)
+// NT threads: 256, or 1024 for a step of few tokens, whose CTAs are too few to hide a row's loads behind one another.
+template <typename TA, typename TH, int NT>
+__global__ void __launch_bounds__(NT)
 hc_norm_kernel(float* __restrict__ x, size_t sstride, int n, const TA* __restrict__ y, int parts, size_t pstride,
                const float* __restrict__ prev, const float* __restrict__ cur, const void* __restrict__ w, int wdt, float eps,
                TH* __restrict__ h, int H, const void* __restrict__ shift_w, int sdt, float* __restrict__ shift_state,
@@ -191,10 +192,11 @@ template <typename TA, typename TH>
 static int launch_hc_norm(size_t smem, cudaStream_t stream, float* x, size_t sstride, int n, const TA* y, int parts, size_t pstride,
                           const float* prev, const float* cur, const void* w, int wdt, float eps, TH* h, int T, int H,
                           const void* shift_w, int sdt, float* shift_state, const int* slot_map, const int* positions) {
-    auto kern = hc_norm_kernel<TA, TH>;
+    const bool wide = T <= 2 * 148 && H >= 1024;
+    auto kern = wide ? hc_norm_kernel<TA, TH, 1024> : hc_norm_kernel<TA, TH, 256>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AIEN_E_STATE;
-    kern<<<T, 256, smem, stream>>>(x, sstride, n, y, parts, pstride, prev, cur, w, wdt, eps, h, H, shift_w, sdt, shift_state, slot_map, positions);
+    kern<<<T, wide ? 1024 : 256, smem, stream>>>(x, sstride, n, y, parts, pstride, prev, cur, w, wdt, eps, h, H, shift_w, sdt, shift_state, slot_map, positions);
     return 0;
 }
 

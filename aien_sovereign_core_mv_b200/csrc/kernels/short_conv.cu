@@ -22,6 +22,9 @@ namespace aien {
 
 constexpr int SC_MAX_TAPS = 8;
 constexpr int SC_THREADS = 256;
+constexpr int SC_THREADS_WIDE = 1024;       // for a step of few tokens: its CTAs are too few to hide a row's loads behind one another
+
+inline int conv_threads(int T, int C) { return (T <= 2 * 148 && C >= 2048) ? SC_THREADS_WIDE : SC_THREADS; }
 
 struct ConvRow {
     int t, first, last, slot;
@@ -74,7 +77,7 @@ __device__ __forceinline__ int conv_rows(int t, int taps, const int* seq_of_toke
 }
 
 template <typename TQ, typename TKV>
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(SC_THREADS_WIDE)
 attn_conv_prepare_kernel(const float* __restrict__ proj, long ld, int q_off, int k_off, int v_off, int Cq, int Ck, int Cv,
                          const void* __restrict__ wq, const void* __restrict__ wk, const void* __restrict__ wv, int wdt, int taps,
                          const void* __restrict__ qn, const void* __restrict__ kn, int ndt, float eps, int G, int V, int value_norm,
@@ -136,7 +139,7 @@ attn_conv_prepare_kernel(const float* __restrict__ proj, long ld, int q_off, int
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
 // out float32 [T, Cq+Ck+Cv] (q | k | v prepared), gb float32 [T, 2*heads] (decay g | beta)
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(SC_THREADS_WIDE)
 delta_conv_prepare_kernel(const float* __restrict__ proj, long ld, int q_off, int k_off, int v_off, int b_off, int a_off,
                           int G, int D, int heads, int V,
                           const void* __restrict__ wq, const void* __restrict__ wk, const void* __restrict__ wv, int wdt, int taps,
@@ -200,7 +203,7 @@ static int launch_attn_conv_prepare(size_t smem, cudaStream_t stream, int T, con
     auto kern = attn_conv_prepare_kernel<TQ, TKV>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AIEN_E_STATE;
-    kern<<<T, SC_THREADS, smem, stream>>>(proj, ld, q_off, k_off, v_off, Cq, Ck, Cv, wq, wk, wv, wdt, taps, qn, kn, ndt, eps, G, V,
+    kern<<<T, conv_threads(T, Cq + Ck + Cv), smem, stream>>>(proj, ld, q_off, k_off, v_off, Cq, Ck, Cv, wq, wk, wv, wdt, taps, qn, kn, ndt, eps, G, V,
                                           value_norm, state, state_slots, seq_of_token, q_start, positions, kv_slots, k_cache, v_cache,
                                           q_out, ldq);
     return 0;
@@ -244,7 +247,7 @@ AIEN_API int aien_delta_conv_prepare(const float* proj, long ld, int q_off, int 
     auto kern = delta_conv_prepare_kernel;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return AIEN_E_STATE;
-    kern<<<T, SC_THREADS, smem, stream>>>(proj, ld, q_off, k_off, v_off, b_off, a_off, G, D, heads, V, wq, wk, wv, w_dt, taps, a_log, dt_bias,
+    kern<<<T, conv_threads(T, 2 * G * D + heads * V), smem, stream>>>(proj, ld, q_off, k_off, v_off, b_off, a_off, G, D, heads, V, wq, wk, wv, w_dt, taps, a_log, dt_bias,
                                           p_dt, state, state_stride, state_slots, seq_of_token, q_start, positions, out, ldo, gb, ldgb);
     return launch_status();
 }
