@@ -136,10 +136,15 @@ delta_rule_kernel(const float* __restrict__ qkv, long ld, int q_off, int k_off, 
     DeltaPieces<DPT, RS> pieces;
     pieces.find(vec, qkv, ld, q_col, k_col, v_col, gb, ldgb, h, heads, D, V, col0);
     pieces.fetch(bufs[0], t0, t1);
-    float Sr[DPT];
+    // the thread's rows of its column, two to a register pair: the sums and the update run on packed pairs
+    // (fma.rn.f32x2, each half rounded as the single operation is), which halves the instructions of the walk
+    float2 Sr[2 * N4];
     const bool fresh = positions[t0] == 0;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) Sr[i] = (!fresh && col_ok && i0 + i < D) ? S[(size_t)(i0 + i) * V + col] : 0.f;
+    for (int i = 0; i < 2 * N4; ++i) {
+        Sr[i].x = (!fresh && col_ok && i0 + 2 * i < D) ? S[(size_t)(i0 + 2 * i) * V + col] : 0.f;
+        Sr[i].y = (!fresh && col_ok && i0 + 2 * i + 1 < D) ? S[(size_t)(i0 + 2 * i + 1) * V + col] : 0.f;
+    }
 
     float4 kc[N4], qc[N4];
     float vj, g, beta;
@@ -161,16 +166,16 @@ delta_rule_kernel(const float* __restrict__ qkv, long ld, int q_off, int k_off, 
         const int n = t1 - t < C::TC ? t1 - t : C::TC;
         take(bufs[b]);
         for (int tt = 0; tt < n; ++tt) {
-            float a[4] = {0.f, 0.f, 0.f, 0.f}, bq[4] = {0.f, 0.f, 0.f, 0.f}, c[4] = {0.f, 0.f, 0.f, 0.f};
+            float2 a0 = make_float2(0.f, 0.f), a1 = a0, b0 = a0, b1 = a0, c0 = a0, c1 = a0;
 #pragma unroll
             for (int i = 0; i < N4; ++i) {
-                const float4 k4 = kc[i], q4 = qc[i];
-                a[0] = fmaf(Sr[4 * i + 0], k4.x, a[0]); bq[0] = fmaf(Sr[4 * i + 0], q4.x, bq[0]); c[0] = fmaf(k4.x, q4.x, c[0]);
-                a[1] = fmaf(Sr[4 * i + 1], k4.y, a[1]); bq[1] = fmaf(Sr[4 * i + 1], q4.y, bq[1]); c[1] = fmaf(k4.y, q4.y, c[1]);
-                a[2] = fmaf(Sr[4 * i + 2], k4.z, a[2]); bq[2] = fmaf(Sr[4 * i + 2], q4.z, bq[2]); c[2] = fmaf(k4.z, q4.z, c[2]);
-                a[3] = fmaf(Sr[4 * i + 3], k4.w, a[3]); bq[3] = fmaf(Sr[4 * i + 3], q4.w, bq[3]); c[3] = fmaf(k4.w, q4.w, c[3]);
+                const float2 k0 = make_float2(kc[i].x, kc[i].y), k1 = make_float2(kc[i].z, kc[i].w);
+                const float2 q0 = make_float2(qc[i].x, qc[i].y), q1 = make_float2(qc[i].z, qc[i].w);
+                a0 = __ffma2_rn(Sr[2 * i], k0, a0); a1 = __ffma2_rn(Sr[2 * i + 1], k1, a1);
+                b0 = __ffma2_rn(Sr[2 * i], q0, b0); b1 = __ffma2_rn(Sr[2 * i + 1], q1, b1);
+                c0 = __ffma2_rn(k0, q0, c0); c1 = __ffma2_rn(k1, q1, c1);
             }
-            float sa = (a[0] + a[1]) + (a[2] + a[3]), sb = (bq[0] + bq[1]) + (bq[2] + bq[3]), sc = (c[0] + c[1]) + (c[2] + c[3]);
+            float sa = (a0.x + a0.y) + (a1.x + a1.y), sb = (b0.x + b0.y) + (b1.x + b1.y), sc = (c0.x + c0.y) + (c1.x + c1.y);
 #pragma unroll
             for (int off = C::CW; off < 32; off <<= 1) {
                 sa += __shfl_xor_sync(0xffffffffu, sa, off);
@@ -180,12 +185,11 @@ delta_rule_kernel(const float* __restrict__ qkv, long ld, int q_off, int k_off, 
             const float gg = g;
             const float u = beta * (vj - gg * sa);
             const float oj = fmaf(sc, u, gg * sb);
+            const float2 g2 = make_float2(gg, gg), u2 = make_float2(u, u);
 #pragma unroll
             for (int i = 0; i < N4; ++i) {
-                Sr[4 * i + 0] = fmaf(kc[i].x, u, gg * Sr[4 * i + 0]);
-                Sr[4 * i + 1] = fmaf(kc[i].y, u, gg * Sr[4 * i + 1]);
-                Sr[4 * i + 2] = fmaf(kc[i].z, u, gg * Sr[4 * i + 2]);
-                Sr[4 * i + 3] = fmaf(kc[i].w, u, gg * Sr[4 * i + 3]);
+                Sr[2 * i] = __ffma2_rn(make_float2(kc[i].x, kc[i].y), u2, __fmul2_rn(g2, Sr[2 * i]));
+                Sr[2 * i + 1] = __ffma2_rn(make_float2(kc[i].z, kc[i].w), u2, __fmul2_rn(g2, Sr[2 * i + 1]));
             }
             if (tt + 1 < n) take(bufs[b] + (tt + 1) * C::ROW);  // the next token's, while this one's output leaves
             if (rs == 0 && col_ok) o[(size_t)(t + tt) * ldo + (size_t)h * V + col] = oj;
@@ -193,8 +197,10 @@ delta_rule_kernel(const float* __restrict__ qkv, long ld, int q_off, int k_off, 
     }
     if (col_ok) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i)
-            if (i0 + i < D) S[(size_t)(i0 + i) * V + col] = Sr[i];
+        for (int i = 0; i < 2 * N4; ++i) {
+            if (i0 + 2 * i < D) S[(size_t)(i0 + 2 * i) * V + col] = Sr[i].x;
+            if (i0 + 2 * i + 1 < D) S[(size_t)(i0 + 2 * i + 1) * V + col] = Sr[i].y;
+        }
     }
 }
 

@@ -63,34 +63,63 @@ hc_norm_kernel(float* __restrict__ x, size_t sstride, int n, const TA* __restric
     if (y != nullptr) hc_load(prev, n, p_in, p_out, p_mix);
     __syncthreads();
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    // four neighbouring columns a thread and pass (16-byte loads and stores of every stream) where the row allows it
+    const bool vec4 = NT == 256 && (H & 3) == 0 && (pstride & 3) == 0;   // the wide CTA of a short step has a thread for every column or two
+    const int step = vec4 ? 4 : 1;
+    for (int c = threadIdx.x * step; c < H; c += blockDim.x * step) {
         const size_t idx = t * H + c;
-        float xs[HC_MAX];
+        float xs[HC_MAX][4];
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s) xs[s] = s < n ? x[(size_t)s * sstride + idx] : 0.f;
+        for (int s = 0; s < HC_MAX; ++s) {
+            if (s < n && vec4) {
+                const float4 v = *reinterpret_cast<const float4*>(x + (size_t)s * sstride + idx);
+                xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w;
+            } else {
+                xs[s][0] = s < n ? x[(size_t)s * sstride + idx] : 0.f;
+                xs[s][1] = xs[s][2] = xs[s][3] = 0.f;
+            }
+        }
         if (y != nullptr) {
-            const float yv = hc_pending(y, parts, pstride, idx);
-            float nx[HC_MAX];
+            float yv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (vec4) {
+                for (int p = 0; p < parts; ++p) {
+                    const float4 v = ld_act4(y + (size_t)p * pstride + idx);
+                    yv[0] += v.x; yv[1] += v.y; yv[2] += v.z; yv[3] += v.w;
+                }
+            } else {
+                yv[0] = hc_pending(y, parts, pstride, idx);
+            }
+            float nx[HC_MAX][4];
 #pragma unroll
             for (int r = 0; r < HC_MAX; ++r) {
                 if (r < n) {
-                    float acc = p_out[r] * yv;
 #pragma unroll
-                    for (int s = 0; s < HC_MAX; ++s)
-                        if (s < n) acc = fmaf(p_mix[s * n + r], xs[s], acc);
-                    nx[r] = acc;
-                    x[(size_t)r * sstride + idx] = acc;
+                    for (int e = 0; e < 4; ++e) {
+                        float acc = p_out[r] * yv[e];
+#pragma unroll
+                        for (int s = 0; s < HC_MAX; ++s)
+                            if (s < n) acc = fmaf(p_mix[s * n + r], xs[s][e], acc);
+                        nx[r][e] = acc;
+                    }
+                    if (vec4) *reinterpret_cast<float4*>(x + (size_t)r * sstride + idx) = make_float4(nx[r][0], nx[r][1], nx[r][2], nx[r][3]);
+                    else x[(size_t)r * sstride + idx] = nx[r][0];
                 }
             }
 #pragma unroll
-            for (int r = 0; r < HC_MAX; ++r) xs[r] = r < n ? nx[r] : 0.f;
-        }
-        float u = 0.f;
+            for (int r = 0; r < HC_MAX; ++r)
 #pragma unroll
-        for (int s = 0; s < HC_MAX; ++s)
-            if (s < n) u = fmaf(c_in[s], xs[s], u);
-        u_s[c] = u;
-        ss = fmaf(u, u, ss);
+                for (int e = 0; e < 4; ++e) xs[r][e] = r < n ? nx[r][e] : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (e >= step) break;
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < HC_MAX; ++s)
+                if (s < n) u = fmaf(c_in[s], xs[s][e], u);
+            u_s[c + e] = u;
+            ss = fmaf(u, u, ss);
+        }
     }
     const float scale = 1.0f / sqrtf(block_sum(ss, red) / (float)H + eps);
     if (shift_w == nullptr) {

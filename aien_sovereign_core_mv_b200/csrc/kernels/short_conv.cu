@@ -34,15 +34,22 @@ struct ConvRow {
 // channel cc of the convolved block that starts at column `off` of proj and at channel `c0` of the state
 __device__ __forceinline__ float conv_value(const float* __restrict__ proj, long ld, int off, int cc, const void* __restrict__ w, int wdt,
                                             int taps, const float* __restrict__ st, int C, int c0, const ConvRow& r) {
-    float y = 0.f;
-    for (int j = 0; j < taps; ++j) {
-        const int tt = r.t - (taps - 1) + j;
-        float u;
-        if (tt >= r.first) u = ld_act(proj + (size_t)tt * ld + off + cc);
-        else if (r.fresh) u = 0.f;
-        else u = st[(size_t)((taps - 1) + (tt - r.first)) * C + c0 + cc];
-        y = fmaf(load_dyn(w, wdt, (size_t)cc * taps + j), u, y);
+    // the taps' loads leave together (a fixed trip count, the taps beyond `taps` masked), then the sum in rising order
+    float u[SC_MAX_TAPS], wv[SC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j) {
+        u[j] = 0.f; wv[j] = 0.f;
+        if (j < taps) {
+            const int tt = r.t - (taps - 1) + j;
+            if (tt >= r.first) u[j] = ld_act(proj + (size_t)tt * ld + off + cc);
+            else if (!r.fresh) u[j] = st[(size_t)((taps - 1) + (tt - r.first)) * C + c0 + cc];
+            wv[j] = load_dyn(w, wdt, (size_t)cc * taps + j);
+        }
     }
+    float y = 0.f;
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j)
+        if (j < taps) y = fmaf(wv[j], u[j], y);
     return y;
 }
 
