@@ -31,25 +31,65 @@ struct ConvRow {
     bool fresh;
 };
 
-// channel cc of the convolved block that starts at column `off` of proj and at channel `c0` of the state
-__device__ __forceinline__ float conv_value(const float* __restrict__ proj, long ld, int off, int cc, const void* __restrict__ w, int wdt,
-                                            int taps, const float* __restrict__ st, int C, int c0, const ConvRow& r) {
-    // the taps' loads leave together (a fixed trip count, the taps beyond `taps` masked), then the sum in rising order
-    float u[SC_MAX_TAPS], wv[SC_MAX_TAPS];
+// The same for a number of taps known when the kernel is compiled: the addresses are one pointer a source and a stride,
+// a token with all its taps inside the step (every token but a portion's first ones) reads without a test, and four
+// bfloat16 weights are one load.  What the kernel spends is instructions, not bytes: with the taps a run-time number
+// it issued several hundred a channel.
+template <int TAPS>
+__device__ __forceinline__ float conv_fixed(const float* __restrict__ proj, long ld, int off, int cc, const void* __restrict__ w, int wdt,
+                                            const float* __restrict__ st, int C, int c0, const ConvRow& r) {
+    const int t_first = r.t - (TAPS - 1);
+    float u[TAPS], wv[TAPS];
+    if (t_first >= r.first) {
+        const float* p = proj + (long)t_first * ld + off + cc;
 #pragma unroll
-    for (int j = 0; j < SC_MAX_TAPS; ++j) {
-        u[j] = 0.f; wv[j] = 0.f;
-        if (j < taps) {
-            const int tt = r.t - (taps - 1) + j;
-            if (tt >= r.first) u[j] = ld_act(proj + (size_t)tt * ld + off + cc);
-            else if (!r.fresh) u[j] = st[(size_t)((taps - 1) + (tt - r.first)) * C + c0 + cc];
-            wv[j] = load_dyn(w, wdt, (size_t)cc * taps + j);
+        for (int j = 0; j < TAPS; ++j) u[j] = __ldcg(p + (long)j * ld);
+    } else {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const int tt = t_first + j;
+            if (tt >= r.first) u[j] = __ldcg(proj + (long)tt * ld + off + cc);
+            else u[j] = r.fresh ? 0.f : st[(long)((TAPS - 1) + (tt - r.first)) * C + c0 + cc];
         }
+    }
+    if (wdt == AIEN_DT_F32) {
+        const float* wf = reinterpret_cast<const float*>(w) + (size_t)cc * TAPS;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wv[j] = wf[j];
+    } else if (TAPS == 4 && (reinterpret_cast<uintptr_t>(w) & 7) == 0) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(w) + (size_t)cc * 4);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        wv[0] = lo.x; wv[1] = lo.y; wv[2 % TAPS] = hi.x; wv[3 % TAPS] = hi.y;
+    } else {
+        const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(w) + (size_t)cc * TAPS;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wv[j] = __bfloat162float(wh[j]);
     }
     float y = 0.f;
 #pragma unroll
-    for (int j = 0; j < SC_MAX_TAPS; ++j)
-        if (j < taps) y = fmaf(wv[j], u[j], y);
+    for (int j = 0; j < TAPS; ++j) y = fmaf(wv[j], u[j], y);
+    return y;
+}
+
+// channel cc of the convolved block that starts at column `off` of proj and at channel `c0` of the state
+__device__ __forceinline__ float conv_value(const float* __restrict__ proj, long ld, int off, int cc, const void* __restrict__ w, int wdt,
+                                            int taps, const float* __restrict__ st, int C, int c0, const ConvRow& r) {
+    switch (taps) {
+        case 2: return conv_fixed<2>(proj, ld, off, cc, w, wdt, st, C, c0, r);
+        case 3: return conv_fixed<3>(proj, ld, off, cc, w, wdt, st, C, c0, r);
+        case 4: return conv_fixed<4>(proj, ld, off, cc, w, wdt, st, C, c0, r);
+        default: break;
+    }
+    float y = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int tt = r.t - (taps - 1) + j;
+        float u;
+        if (tt >= r.first) u = ld_act(proj + (size_t)tt * ld + off + cc);
+        else if (r.fresh) u = 0.f;
+        else u = st[(size_t)((taps - 1) + (tt - r.first)) * C + c0 + cc];
+        y = fmaf(load_dyn(w, wdt, (size_t)cc * taps + j), u, y);
+    }
     return y;
 }
 
