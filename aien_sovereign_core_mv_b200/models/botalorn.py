@@ -74,8 +74,15 @@ def _window(mixer: Mapping[str, Any]) -> int:
     return int((mixer.get("mask") or {}).get("size") or 0)
 
 
+def _heads_divide(mixer: Mapping[str, Any], where: str) -> None:
+    heads, kv = _need(mixer, "heads", where, int), _need(mixer, "kv_heads", where, int)
+    if heads <= 0 or kv <= 0 or heads % kv:
+        raise ConfigError(f"config.json: {where}.heads {heads} must be a positive multiple of {where}.kv_heads {kv}")
+
+
 def _attention(i: int, mixer: Mapping[str, Any], width: int, eps: float, cache_window: int):
     where = f"layers[{i}].mixer"
+    _heads_divide(mixer, where)
     own = mixer.get("kv_from") is None
     params = {
         "hidden_size": width, "num_heads": _need(mixer, "heads", where, int), "num_kv_heads": _need(mixer, "kv_heads", where, int),
@@ -92,6 +99,7 @@ def _attention(i: int, mixer: Mapping[str, Any], width: int, eps: float, cache_w
 
 def _delta(i: int, mixer: Mapping[str, Any], width: int, eps: float, _cw: int):
     where = f"layers[{i}].mixer"
+    _heads_divide(mixer, where)
     params = {"hidden_size": width, "num_heads": _need(mixer, "heads", where, int), "num_qk_heads": _need(mixer, "kv_heads", where, int),
               "head_dim": _need(mixer, "dim", where, int), "value_dim": int(mixer.get("vdim") or mixer["dim"]),
               "taps": int(mixer.get("conv") or 1), "norm_eps": eps}
