@@ -42,18 +42,20 @@ template <int AR, int BN> struct TcT {
 };
 
 __device__ __forceinline__ float tc_gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+__device__ __forceinline__ float tc_relu2(float z) { return z > 0.f ? z * z : 0.f; }
 __device__ __forceinline__ float tc_gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 
 // Stores 32 consecutive accumulator columns of one row: r holds columns n0+c0 .. +31 of row `row`.
 // EPI 0: as they are; EPI 1: silu(gate)*up over columns interleaved in runs of 8 (out has N/2 columns);
-// EPI 2 / 3: the gelu in its erf / tanh form of every value.
+// EPI 2 / 3: the gelu in its erf / tanh form of every value; EPI 4: the square of relu.
 template <int EPI, typename TC>
 __device__ __forceinline__ void tc_store_chunk(const uint32_t r_in[32], TC* __restrict__ out, long ldc, int row, int n0, int c0, int N) {
                 uint32_t r[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     r[j] = EPI == 2 ? __float_as_uint(tc_gelu_erf(__uint_as_float(r_in[j])))
-                                    : (EPI == 3 ? __float_as_uint(tc_gelu_tanh(__uint_as_float(r_in[j]))) : r_in[j]);
+                                    : (EPI == 3 ? __float_as_uint(tc_gelu_tanh(__uint_as_float(r_in[j])))
+                                                : (EPI == 4 ? __float_as_uint(tc_relu2(__uint_as_float(r_in[j]))) : r_in[j]));
                 if (EPI != 1) {
                     TC* dst = out + (size_t)row * ldc + n0 + c0;
                     const int valid = N - (n0 + c0);
@@ -829,7 +831,7 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
     if ((lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return AIEN_E_ALIGN;
     if (epilogue == 1 && (N & 15)) return AIEN_E_SHAPE;
     if ((M + TC_BM - 1) / TC_BM > 2147483647 / 1 || (N + 95) / 96 > 65535) return AIEN_E_SHAPE;
-    if (epilogue == 2 || epilogue == 3) {          // gelu (erf / tanh form) of every value, bfloat16 out, K in one range
+    if (epilogue == 2 || epilogue == 3 || epilogue == 4) {   // gelu (erf / tanh form) or relu squared of every value, bfloat16 out, K in one range
         if (c_dt != AIEN_DT_BF16 || splits != 1) return AIEN_E_SHAPE;
         const int plan = tc_plan(M, N, 1);
         const int wide = plan == 256 ? tc_m256_cols(M, N, K, 1) : 0;
@@ -837,6 +839,11 @@ AIEN_API int aien_gemm_tc(const void* A, long lda, const void* W, long ldw, void
             if (wide > 0) return launch_tc_persistent_m256<2, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
             if (plan == 256) return launch_tc_persistent<256, 2, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, 1, 0, stream);
             return launch_tc<2, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
+        }
+        if (epilogue == 4) {
+            if (wide > 0) return launch_tc_persistent_m256<4, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
+            if (plan == 256) return launch_tc_persistent<256, 4, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, 1, 0, stream);
+            return launch_tc<4, __nv_bfloat16>(A, lda, W, ldw, out, ldc, 1, 0, M, N, K, stream);
         }
         if (wide > 0) return launch_tc_persistent_m256<3, __nv_bfloat16>(wide, A, lda, W, ldw, out, ldc, M, N, K, stream);
         if (plan == 256) return launch_tc_persistent<256, 3, __nv_bfloat16>(A, lda, W, ldw, out, ldc, M, N, K, 1, 0, stream);

@@ -239,6 +239,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     } else if (EPI == 4) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) sum[i] = 0.5f * sum[i] * (1.0f + tanhf(0.7978845608028654f * (sum[i] + 0.044715f * sum[i] * sum[i] * sum[i])));
+                    } else if (EPI == 5) {                                   // the square of relu
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) sum[i] = sum[i] > 0.f ? sum[i] * sum[i] : 0.f;
                     }
                     if (r0 < N) {
                         if (t0 < M) o[(size_t)t0 * ldc + r0] = from_f<TC>(sum[0]);
@@ -337,6 +340,7 @@ static int gemv_stream_dispatch(const void* a, long lda, const void* W, long ldw
     if (epilogue == 2) { if (M <= 8) GS_CASE(1, 2, float); else GS_CASE(2, 2, float); }
     if (epilogue == 3 && c_dt == AIEN_DT_BF16 && splits == 1) { if (M <= 8) GS_CASE(1, 3, __nv_bfloat16); else GS_CASE(2, 3, __nv_bfloat16); }
     if (epilogue == 4 && c_dt == AIEN_DT_BF16 && splits == 1) { if (M <= 8) GS_CASE(1, 4, __nv_bfloat16); else GS_CASE(2, 4, __nv_bfloat16); }
+    if (epilogue == 5 && c_dt == AIEN_DT_BF16 && splits == 1) { if (M <= 8) GS_CASE(1, 5, __nv_bfloat16); else GS_CASE(2, 5, __nv_bfloat16); }
 #undef GS_CASE
     return AIEN_E_SHAPE;
 }
@@ -346,7 +350,7 @@ static int gemv_stream_dispatch(const void* a, long lda, const void* W, long ldw
 // partial products are written as zeros.
 AIEN_API int aien_gemv_stream_bf16(const void* a, long lda, const void* W, long ldw, void* out, int c_dt, long ldc,
                                    int M, int N, int K, int epilogue, int splits, size_t part_stride, cudaStream_t stream) {
-    if (epilogue != 0 && epilogue != 1 && epilogue != 3 && epilogue != 4) return AIEN_E_SHAPE;    // 3 / 4: gelu (erf / tanh form), bfloat16 out
+    if (epilogue != 0 && epilogue != 1 && epilogue != 3 && epilogue != 4 && epilogue != 5) return AIEN_E_SHAPE;    // 3 / 4: gelu (erf / tanh form), 5: relu squared; bfloat16 out
     GsFuse none = {};
     return gemv_stream_dispatch(a, lda, W, ldw, out, c_dt, ldc, M, N, K, epilogue, splits, part_stride, none, stream);
 }

@@ -458,7 +458,7 @@ def qk_rope_pairs_unit_kv_write(q: torch.Tensor, k: Optional[torch.Tensor], v: O
 
 # ---------------------------------------------------------------------------- routed feed-forward
 ACT_KINDS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "relu2": 2}      # relu2: the square of relu
-ACT_IN_PRODUCT = (0, 1)             # the kinds that the products' epilogues know; the others run as a kernel behind the product
+ACT_IN_PRODUCT = (0, 1, 2)          # the kinds that the products' epilogues know; others would run as a kernel behind the product
 
 
 def moe_route(z: torch.Tensor, groups: int, keep: int, top: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor,
@@ -575,7 +575,7 @@ def moe_experts(ctx, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, 
 
 
 def act_rows(a: torch.Tensor, act_kind: int) -> None:
-    """a = f(a) in place: 0 the erf gelu, 1 the tanh gelu."""
+    """a = f(a) in place: 0 the erf gelu, 1 the tanh gelu, 2 the square of relu."""
     _dev(a)
     assert a.is_contiguous()
     _check(lib().aien_act_rows(_p(a), dt(a), a.numel(), int(act_kind), _stream()), "act_rows")
@@ -690,7 +690,7 @@ def gemv_splits(N: int, K_: int) -> int:
 def gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
     """out = a . w^T for up to 16 rows of a (bfloat16, float32 accumulation).  ``epilogue=1``:
     w holds gate|up rows interleaved in groups of 8 and out = silu(gate)*up with N/2 columns.
-    ``epilogue=3`` / ``4`` (the streamed kernel, bfloat16 out): the gelu in its erf / tanh form of every value.
+    ``epilogue=3`` / ``4`` / ``5`` (the streamed kernel, bfloat16 out): the gelu in its erf / tanh form, the square of relu.
     ``out`` of shape [P, M, N] float32 receives P partial products over P ranges of K."""
     _dev(a, w, out)
     M, K_ = a.shape
@@ -727,7 +727,8 @@ def gemm_tc_supports(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> None:
     """out = a . w^T on the tcgen05 tensor cores (bfloat16 operands, float32 accumulation in
     tensor memory).  ``epilogue=1``: w holds gate|up rows interleaved in runs of 8 and
-    out = silu(gate)*up with N/2 columns.  ``epilogue=2`` / ``3`` (bfloat16 out): the gelu in its erf / tanh form."""
+    out = silu(gate)*up with N/2 columns.  ``epilogue=2`` / ``3`` / ``4`` (bfloat16 out): the gelu in its erf / tanh
+    form, the square of relu."""
     _dev(a, w, out)
     M, K_ = a.shape
     N = w.shape[0]

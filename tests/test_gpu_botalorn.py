@@ -500,6 +500,31 @@ def test_norm_per_head_with_a_shared_weight_and_gate(dtype, groups, group, act):
 
 
 # ------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("rows,n,k", [(1, 192, 128), (7, 320, 256), (16, 96, 64), (40, 192, 128), (300, 384, 192), (2048, 512, 256)])
+def test_relu_squared_in_the_products_epilogue(rows, n, k):
+    """W_up h followed by the square of relu, as the feed-forward's first product leaves it in bfloat16: the streamed
+    product for few rows and the tensor-core product for many apply it to the float32 sums before they are rounded."""
+    from aien_sovereign_core_mv_b200 import kernels as K
+    g = torch.Generator().manual_seed(rows + n)
+    a = (torch.randn(rows, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) * 0.2).to(torch.bfloat16).cuda()
+    z = a.float().cpu().double().numpy() @ w.float().cpu().double().numpy().T
+    want = np.where(z > 0, z * z, 0.0)
+    out = torch.zeros(rows, n, dtype=torch.bfloat16).cuda()
+    act = K.ACT_KINDS["relu2"]
+    assert act in K.ACT_IN_PRODUCT
+    if rows <= 16:
+        assert K.gemv_takes_activation(k)
+        K.gemv(a, w, out, epilogue=3 + act)
+    else:
+        assert K.gemm_tc_supports(a, w, out)
+        K.gemm_tc(a, w, out, epilogue=2 + act)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    assert (got >= 0).all() and (got[z < -1e-3] == 0).all()
+    H.assert_close(got, want, 1e-2, f"relu squared behind a product of {rows} rows")
+
+
 @pytest.mark.parametrize("which", list(CONFIGS))
 def test_layers_of_a_short_request_float32(models, which):
     """The sum of the streams after every layer, so that a fault names its layer.  A block leaves its last write pending;
