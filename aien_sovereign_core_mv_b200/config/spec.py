@@ -54,6 +54,9 @@ class RunEntry:
     layer: int                      # index into ModelSpec.layers
     cache: int                      # cache slot this run attends over (-1: the mixer keeps none)
     writes_cache: bool = True       # False: read a slot that an earlier run wrote
+    # >= 0: this run opens pass number ``enter`` of a repeated stretch of layers; the model's ``pass_input`` part is
+    # applied to the stream right before it
+    enter: int = -1
 
 
 @dataclass(frozen=True)
@@ -74,6 +77,8 @@ class ModelSpec:
     # is float32 [streams, T, hidden]: the embedding fills the first copy, the decoder repeats it into the others, and
     # the rows that reach the final norm are the sum of the copies; every block must be of a kind that takes them.
     streams: int = 1
+    # family "pass_input": what is added to the stream before the runs that carry ``enter`` (None: the model has none)
+    pass_input: Optional[PartSpec] = None
 
     def validate(self) -> None:
         n = len(self.layers)
@@ -81,6 +86,8 @@ class ModelSpec:
         for i, run in enumerate(self.run_list):
             if not (0 <= run.layer < n):
                 raise ValueError(f"run_list[{i}] names layer {run.layer}, model has {n}")
+            if run.enter >= 0 and self.pass_input is None:
+                raise ValueError(f"run_list[{i}] opens pass {run.enter} and the model names no pass_input part")
             if run.cache < 0:
                 continue
             if run.writes_cache:

@@ -5,7 +5,8 @@
 // no value), values of their own size `hdv` <= head size, optionally only the tokens that
 // `token_list` names (T of them).  Optional per head: a factor on the scaled score (`head_scale`), a distance bias
 // (`slopes`: slope[h] * (query position - key position) is taken off the score) and an output gate (`gate` float32
-// [T, ldg]: the head's output is multiplied by sigmoid(gate[t][h])).
+// [T, ldg]: the head's output is multiplied by sigmoid(gate[t][h])).  `softcap` c > 0: the scaled score s becomes
+// c * tanh(s / c) before the other terms.
 //
 // It serves the true-32-bit engine for every kind of step (whole prompts, portions with an
 // offset, single decoded tokens) and is the plain kernel the faster attention kernels are
@@ -32,7 +33,7 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                                int nq, int nkv, int hd, int page_size, int window, float scale,
                                int chunk, const float* __restrict__ sinks, int hdv, const int* __restrict__ token_list,
                                const float* __restrict__ head_scale, const float* __restrict__ slopes,
-                               const float* __restrict__ gate, long ldg) {
+                               const float* __restrict__ gate, long ldg, float softcap) {
     __shared__ float qs[256];
     __shared__ float p[AG_THREADS];
     __shared__ int slots[AG_THREADS];
@@ -63,6 +64,7 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
                 float dot = 0.f;
                 for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f(kp[d]), dot);
                 score = dot * scale;
+                if (softcap > 0.f) score = softcap * tanhf(score / softcap);
                 if (head_scale) score *= hscale;
                 if (slopes) score -= slope * (float)(pos - j);
             }
@@ -114,7 +116,7 @@ AIEN_API int aien_paged_attention_generic(
     const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
     void* out, long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale,
     int act_dt, int kv_dt, int T, int chunk, const float* sinks, int hdv, const int* token_list,
-    const float* head_scale, const float* slopes, const float* gate, long ldg, cudaStream_t stream) {
+    const float* head_scale, const float* slopes, const float* gate, long ldg, float softcap, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (hdv <= 0) hdv = hd;
     if (hd <= 0 || hd > 256 || hdv > 256 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || chunk < 0) return AIEN_E_SHAPE;
@@ -124,6 +126,6 @@ AIEN_API int aien_paged_attention_generic(
         (paged_attention_generic_kernel<TQ, TKV, TQ><<<grid, AG_THREADS, 0, stream>>>(
             (const TQ*)q, q_stride, (const TKV*)k_cache, (const TKV*)v_cache, block_table, max_blocks,
             seq_of_token, positions, (TQ*)out, out_stride, nq, nkv, hd, page_size, window, scale, chunk, sinks, hdv, token_list,
-            head_scale, slopes, gate, ldg))));
+            head_scale, slopes, gate, ldg, softcap))));
     return launch_status();
 }

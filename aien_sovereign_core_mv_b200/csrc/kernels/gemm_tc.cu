@@ -316,6 +316,9 @@ gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             } else if (EPI == 3) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(tc_gelu_tanh(__uint_as_float(r[j])));
+            } else if (EPI == 4) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(tc_relu2(__uint_as_float(r[j])));
             }
             if (row_dest != nullptr) {
 #pragma unroll
@@ -901,10 +904,12 @@ AIEN_API int aien_gemm_tc_grouped(const void* A, long lda, const void* W, long l
         if (epilogue == 0) TCG_CASE(0, __nv_bfloat16);
         if (epilogue == 2) TCG_CASE(2, __nv_bfloat16);
         if (epilogue == 3) TCG_CASE(3, __nv_bfloat16);
+        if (epilogue == 4) TCG_CASE(4, __nv_bfloat16);
     } else if (c_dt == AIEN_DT_F32) {
         if (epilogue == 0) TCG_CASE(0, float);
         if (epilogue == 2) TCG_CASE(2, float);
         if (epilogue == 3) TCG_CASE(3, float);
+        if (epilogue == 4) TCG_CASE(4, float);
     } else {
         return AIEN_E_DTYPE;
     }

@@ -95,6 +95,65 @@ moe_route_kernel(const float* __restrict__ z, int E, int groups, int keep, int t
     }
 }
 
+// The router with a correction on the choice and experts that return their input.  s = softmax(z[t][0..E)) (rows ldz
+// apart); the `top` experts with the largest s + correction are chosen (ties to the lower index); a choice weighs s,
+// divided by the sum of the chosen s plus renorm_eps when `renorm` is set.  Experts from `real` on have no tensors:
+// their output is their input, so their weights are summed into w_same[t] and the choice is handed on as expert 0
+// with weight zero (the expert products need no case for it).  One warp per token.
+__global__ void __launch_bounds__(32)
+moe_route_biased_kernel(const float* __restrict__ z, long ldz, int E, int real, int top, int renorm, float renorm_eps,
+                        const void* __restrict__ correction, int cdt, int* __restrict__ ids, float* __restrict__ wts,
+                        float* __restrict__ w_same, int* __restrict__ expert_count) {
+    __shared__ float s[ROUTE_MAX_EXPERTS];
+    __shared__ float ch[ROUTE_MAX_EXPERTS];
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float* zr = z + (size_t)t * ldz;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) { const float v = zr[e]; s[e] = v; m = fmaxf(m, v); }
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - m); s[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+        s[e] *= inv;
+        ch[e] = correction != nullptr ? s[e] + load_dyn(correction, cdt, e) : s[e];
+    }
+    __syncwarp();
+    float wsum = 0.f;
+    for (int r = 0; r < top; ++r) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) if (ch[e] > bv) { bv = ch[e]; bi = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        const float w = s[bi];
+        wsum += w;
+        __syncwarp();
+        if (lane == 0) {
+            ids[(size_t)t * top + r] = bi;
+            wts[(size_t)t * top + r] = w;
+            ch[bi] = -INFINITY;                            // taken
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float div = renorm ? wsum + renorm_eps : 1.0f;
+        float same = 0.f;
+        for (int r = 0; r < top; ++r) {
+            const size_t at = (size_t)t * top + r;
+            const float w = wts[at] / div;
+            int e = ids[at];
+            if (e >= real) { same += w; e = 0; wts[at] = 0.f; } else wts[at] = w;
+            ids[at] = e;
+            if (expert_count != nullptr) atomicAdd(expert_count + e, 1);
+        }
+        if (w_same != nullptr) w_same[t] = same;
+    }
+}
+
 // ---------------------------------------------------------------- plain expert products
 // One warp per output value; 8 warps a CTA take 8 consecutive output rows of one (token, choice).
 template <typename TH, typename TW, typename TO>
@@ -303,6 +362,17 @@ AIEN_API int aien_moe_route(const float* z, int T, int E, int groups, int keep, 
     if (E <= 0 || E > ROUTE_MAX_EXPERTS || groups <= 0 || E % groups != 0 || keep <= 0 || keep > groups || top <= 0 ||
         top > keep * (E / groups)) return AIEN_E_SHAPE;
     launch_chain(moe_route_kernel, dim3(T), dim3(32), 0, stream, z, E, groups, keep, top, renorm, ids, wts, expert_count);
+    return launch_status();
+}
+
+// z float32 [T, ldz]: the first E numbers of a row are the router's; correction [E] in c_dt (or null); experts from
+// `real` on return their input (w_same float32 [T], needed when real < E).
+AIEN_API int aien_moe_route_biased(const float* z, long ldz, int T, int E, int real, int top, int renorm, float renorm_eps,
+                                   const void* correction, int c_dt, int* ids, float* wts, float* w_same, int* expert_count,
+                                   cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > ROUTE_MAX_EXPERTS || real <= 0 || real > E || top <= 0 || top > E || (real < E && w_same == nullptr)) return AIEN_E_SHAPE;
+    moe_route_biased_kernel<<<T, 32, 0, stream>>>(z, ldz, E, real, top, renorm, renorm_eps, correction, c_dt, ids, wts, w_same, expert_count);
     return launch_status();
 }
 

@@ -237,6 +237,30 @@ delta_conv_prepare_kernel(const float* __restrict__ proj, long ld, int q_off, in
     }
 }
 
+// One block of C convolved channels with a bias and an activation of its own:
+// out[t][c] = f(conv(c) + bias[c]), f the identity (act 0) or silu (act 1); float32 out.
+__global__ void __launch_bounds__(SC_THREADS_WIDE)
+conv_act_kernel(const float* __restrict__ proj, long ld, int off, int C, const void* __restrict__ w, int wdt,
+                const void* __restrict__ bias, int bdt, int taps, int act, float* __restrict__ state, size_t state_stride,
+                const int* __restrict__ state_slots, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
+                const int* __restrict__ positions, float* __restrict__ out, long ldo) {
+    ConvRow r;
+    const int rows = conv_rows(blockIdx.x, taps, seq_of_token, q_start, positions, state_slots, r);
+    if (rows == 0) return;
+    float* st = state + (size_t)r.slot * state_stride;
+    const int t0 = r.t;
+    for (int i = 0; i < rows; ++i) {
+        r.t = t0 + i;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float y = conv_value(proj, ld, off, c, w, wdt, taps, st, C, 0, r);
+            if (bias != nullptr) y += load_dyn(bias, bdt, c);
+            out[(size_t)r.t * ldo + c] = act == 1 ? silu_f(y) : y;
+        }
+    }
+    __syncthreads();
+    if (t0 == r.first && taps > 1) conv_state_update(proj, ld, off, C, taps, st, C, 0, r);
+}
+
 }  // namespace aien
 
 using namespace aien;
@@ -296,5 +320,18 @@ AIEN_API int aien_delta_conv_prepare(const float* proj, long ld, int q_off, int 
         return AIEN_E_STATE;
     kern<<<T, conv_threads(T, 2 * G * D + heads * V), smem, stream>>>(proj, ld, q_off, k_off, v_off, b_off, a_off, G, D, heads, V, wq, wk, wv, w_dt, taps, a_log, dt_bias,
                                           p_dt, state, state_stride, state_slots, seq_of_token, q_start, positions, out, ldo, gb, ldgb);
+    return launch_status();
+}
+
+// proj float32 [T, ld] with the C convolved channels from column `off` on; weights [C, taps] in w_dt, bias [C] in b_dt (or
+// null); state float32 rows of state_stride numbers whose first (taps-1)*C are the convolution's; out float32 [T, ldo].
+AIEN_API int aien_conv_act(const float* proj, long ld, int off, int C, const void* w, int w_dt, const void* bias, int b_dt, int taps,
+                           int act, float* state, size_t state_stride, const int* state_slots, const int* seq_of_token,
+                           const int* q_start, const int* positions, float* out, long ldo, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (taps < 1 || taps > SC_MAX_TAPS || C <= 0 || (act != 0 && act != 1)) return AIEN_E_SHAPE;
+    if (taps > 1 && state == nullptr) return AIEN_E_SHAPE;
+    conv_act_kernel<<<T, conv_threads(T, C), 0, stream>>>(proj, ld, off, C, w, w_dt, bias, b_dt, taps, act, state, state_stride, state_slots,
+                                                          seq_of_token, q_start, positions, out, ldo);
     return launch_status();
 }

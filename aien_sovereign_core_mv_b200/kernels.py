@@ -117,7 +117,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_qk_norm_rope_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, P, P, I, F, P, P, I, P, P, P, I, I, I, P],
         "aien_convert": [P, I, P, I, c_size_t, P],
         "aien_gemm_simple": [P, I, L, P, I, L, P, I, L, I, I, I, P],
-        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P, P, P, P, L, P],
+        "aien_paged_attention_generic": [P, L, P, P, P, I, P, P, P, L, I, I, I, I, I, F, I, I, I, I, P, I, P, P, P, P, L, F, P],
         "aien_branch_norm_add": [P, P, I, I, c_size_t, P, I, I, c_size_t, P, I, F, P, I, I, I, P],
         "aien_stream_norm_inplace": [P, P, I, F, P, I, I, I, P],
         "aien_qk_rope_pairs_unit_kv_write": [P, L, I, P, L, P, L, I, I, I, c_size_t, P, L, I, I, I, F, P, P, I, P, P, P, I, I, I, P],
@@ -186,6 +186,17 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_grouped_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, I, I, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
+        "aien_conv_act": [P, L, I, I, P, I, P, I, I, I, P, c_size_t, P, P, P, P, P, L, I, P],
+        "aien_selective_scan": [P, L, P, L, P, L, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, I, L, I, I, I, I, I, I, P, P],
+        "aien_ssd_scan": [P, L, I, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, L, I, I, I, I, I, I, I, I, P, P],
+        "aien_gate_group_norm": [P, L, P, L, P, I, F, F, P, I, L, I, I, I, P],
+        "aien_scaled_add_rmsnorm": [P, P, I, I, c_size_t, P, P, P, I, F, P, I, I, I, P],
+        "aien_pass_input": [P, P, P, I, I, I, P],
+        "aien_clamped_glu": [P, I, L, I, I, P, P, I, F, F, P, I, L, I, I, P],
+        "aien_sigmoid_gate": [P, I, L, P, L, F, P, I, L, I, I, P],
+        "aien_routed_combine": [P, I, I, c_size_t, P, I, L, P, P, I, I, c_size_t, P, L, P, I, I, P],
+        "aien_moe_route_biased": [P, L, I, I, I, I, I, F, P, I, P, P, P, P, P],
+        "aien_rope_halves_value_write": [P, L, I, I, I, I, I, I, I, P, P, I, P, P, I, L, P, P, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(l, name)
@@ -606,7 +617,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
                             scale: float, chunk: int = 0, sinks: Optional[torch.Tensor] = None, value_dim: int = 0,
                             token_list: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None,
                             head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
-                            gate: Optional[torch.Tensor] = None) -> None:
+                            gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Causal attention of T query tokens over their requests' pages.  q [T, nq*hd] (row stride
     free), caches [slots, nkv, hd], block_table int32 [S, max_blocks], out [T, nq*hd].
     ``chunk`` > 0: a token sees only the keys of its own chunk of that many positions.  ``sinks``
@@ -614,7 +625,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     size of a value when it differs from the head size (v_cache [slots, nkv, value_dim], out [T, nq*value_dim]).
     ``token_list`` (int32) with ``num_tokens``: only these tokens of the step are served.  Per head (float32 [nq]):
     ``head_scale`` multiplies the scaled score, ``slopes`` takes slope * (query position - key position) off it;
-    ``gate`` (float32 [T, >= nq], row stride free): the head's output is multiplied by sigmoid(gate[t, h])."""
+    ``gate`` (float32 [T, >= nq], row stride free): the head's output is multiplied by sigmoid(gate[t, h]).
+    ``softcap`` c > 0: the scaled score s becomes c * tanh(s / c)."""
     _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, sinks, token_list, head_scale, slopes, gate)
     for v in (head_scale, slopes):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == num_q_heads)
@@ -630,7 +642,7 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
         _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
         _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim, page_size, window, float(scale),
         dt(q), dt(k_cache), T, int(chunk), _p(sinks), int(value_dim), _p(token_list), _p(head_scale), _p(slopes), _p(gate),
-        gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_generic")
+        gate.stride(0) if gate is not None else 0, float(softcap or 0.0), _stream()), "paged_attention_generic")
 
 
 # ---------------------------------------------------------------------------- sampling
@@ -1690,3 +1702,232 @@ def biased_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
         return
     paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
                             num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim, **terms)
+
+
+# ---------------------------------------------------------------------------- state-space recurrences
+def conv_act(proj: torch.Tensor, off: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor], taps: int, act: str,
+             state: Optional[torch.Tensor], slot_map: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
+             positions: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = f(sum_j w[c, j] * u[t - taps + 1 + j, c] + bias[c]) for the ``channels`` columns of the float32 rows
+    ``proj`` [T, *] from column ``off`` on; f the identity ("none") or silu.  Rows before a portion come from the
+    request's state row (its first (taps - 1) * channels numbers, the newest row last; zeros at a sequence's start),
+    which is rewritten with the portion's last rows.  out float32 [T, >= channels]."""
+    _dev(proj, w, bias, state, slot_map, seq_of_token, q_start, positions, out)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1
+    assert w.is_contiguous() and tuple(w.shape) == (channels, taps) and (bias is None or (bias.is_contiguous() and bias.numel() == channels))
+    assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.stride(-1) == 1 and state.shape[-1] >= (taps - 1) * channels)
+    _check(lib().aien_conv_act(_p(proj), proj.stride(0), int(off), int(channels), _p(w), dt(w), _p(bias), dt(bias) if bias is not None else F32,
+                               int(taps), {"none": 0, "silu": 1}[act], _p(state), state.stride(0) if state is not None else 0, _p(slot_map),
+                               _p(seq_of_token), _p(q_start), _p(positions), _p(out), out.stride(0), T, _stream()), "conv_act")
+
+
+SCAN_SEGMENT_MIN_TOKENS = 128        # steps with fewer tokens walk every portion in one piece
+
+
+def scan_segments(num_tokens: int, decode_only: bool) -> tuple:
+    """(segment length, most segments a portion has) for the portion-parallel recurrences of a step; (0, 1): one piece.
+    It depends on the step's token count alone, so that steps of equal shape launch alike."""
+    if decode_only or num_tokens < SCAN_SEGMENT_MIN_TOKENS:
+        return 0, 1
+    seg = 64
+    while seg * 32 < num_tokens:
+        seg *= 2
+    return seg, (num_tokens + seg - 1) // seg
+
+
+def scan_scratch_floats(max_tokens: int, max_seqs: int, lanes: int) -> int:
+    """Upper bound of the float32 scratch the portion-parallel recurrences take for ``lanes`` state values a request."""
+    worst = 0
+    t = SCAN_SEGMENT_MIN_TOKENS
+    while True:
+        tt = min(t, max_tokens)
+        seg, _ = scan_segments(tt, False)
+        if seg:
+            worst = max(worst, 2 * (tt // seg + max_seqs) * lanes)
+        if t >= max_tokens:
+            return worst
+        t *= 2
+
+
+def selective_scan(x: torch.Tensor, dtz: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor, A: torch.Tensor,
+                   dt_bias: torch.Tensor, D: torch.Tensor, state: torch.Tensor, s_off: int, slot_map: torch.Tensor, q_start: torch.Tensor,
+                   positions: torch.Tensor, out: torch.Tensor, num_seqs: int, N: int, seg_len: int = 0, nseg: int = 1,
+                   scratch: Optional[torch.Tensor] = None) -> None:
+    """The selective scan over every request's portion: per channel c and state n, token by token,
+    dt = softplus(dtz[c] + dt_bias[c]); S[c, n] = exp(dt * A[c, n]) * S[c, n] + dt * x[c] * B[n]; y[c] = sum_n S[c, n] * C[n]
+    + D[c] * x[c]; out[c] = y[c] * silu(z[c]).  x, dtz, z float32 [T, inner] (row strides free); B and C are the N numbers
+    from columns ``b_off`` / ``c_off`` of the float32 rows ``bc``; A float32 [inner, N]; S lives in the request's state row
+    from ``s_off`` on ([inner, N]) and starts from zeros where a portion's first token has position 0."""
+    _dev(x, dtz, bc, z, A, dt_bias, D, state, slot_map, q_start, positions, out, scratch)
+    T, inner = x.shape
+    for t in (x, dtz, bc, z):
+        assert t.dtype == torch.float32 and t.stride(1) == 1
+    assert A.dtype == torch.float32 and A.is_contiguous() and tuple(A.shape) == (inner, N) and dt_bias.dtype == D.dtype
+    assert dt_bias.is_contiguous() and D.is_contiguous() and state.dtype == torch.float32 and state.stride(-1) == 1 and out.stride(1) == 1
+    if seg_len and nseg > 1:
+        assert scratch is not None and scratch.numel() >= 2 * (T // seg_len + num_seqs) * inner * N
+    _check(lib().aien_selective_scan(_p(x), x.stride(0), _p(dtz), dtz.stride(0), _p(bc), bc.stride(0), int(b_off), int(c_off), _p(z), z.stride(0),
+                                     _p(A), _p(dt_bias), _p(D), dt(D), _p(state), state.stride(0), int(s_off), _p(slot_map), _p(q_start),
+                                     _p(positions), _p(out), dt(out), out.stride(0), T, int(num_seqs), inner, int(N), int(seg_len), int(nseg),
+                                     _p(scratch), _stream()), "selective_scan")
+    if seg_len and nseg > 1:
+        add_launches(2)
+
+
+def ssd_scan(xbc: torch.Tensor, x_off: int, b_off: int, c_off: int, dtr: torch.Tensor, A: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
+             state: torch.Tensor, s_off: int, slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, y: torch.Tensor,
+             num_seqs: int, heads: int, V: int, G: int, N: int, seg_len: int = 0, nseg: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+    """The state-space-duality recurrence over every request's portion: per head h (group g = h // (heads // G)), token by
+    token, dt = softplus(dtr[h] + dt_bias[h]); S = exp(-A[h] * dt) * S + dt * B[g] x[h]^T (S is N x V); y[h] = S^T C[g] +
+    D[h] * x[h].  x, B, C are column blocks of the float32 rows ``xbc``; dtr float32 [T, heads] (row stride free); A float32
+    [heads]; S lives in the request's state row from ``s_off`` on ([heads, N, V]); y float32 [T, heads * V]."""
+    _dev(xbc, dtr, A, dt_bias, D, state, slot_map, q_start, positions, y, scratch)
+    T = xbc.shape[0]
+    assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and dtr.dtype == torch.float32 and dtr.stride(1) == 1
+    assert A.dtype == torch.float32 and A.numel() == heads and dt_bias.dtype == D.dtype and dt_bias.is_contiguous() and D.is_contiguous()
+    assert state.dtype == torch.float32 and state.stride(-1) == 1 and y.dtype == torch.float32 and y.stride(1) == 1
+    if seg_len and nseg > 1:
+        assert scratch is not None and scratch.numel() >= 2 * (T // seg_len + num_seqs) * heads * N * V
+    _check(lib().aien_ssd_scan(_p(xbc), xbc.stride(0), int(x_off), int(b_off), int(c_off), _p(dtr), dtr.stride(0), _p(A), _p(dt_bias), _p(D),
+                               dt(D), _p(state), state.stride(0), int(s_off), _p(slot_map), _p(q_start), _p(positions), _p(y), y.stride(0),
+                               T, int(num_seqs), int(heads), int(V), int(G), int(N), int(seg_len), int(nseg), _p(scratch), _stream()), "ssd_scan")
+    if seg_len and nseg > 1:
+        add_launches(2)
+
+
+def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, mult: float, out: torch.Tensor, groups: int) -> None:
+    """out = (y * silu(z)) / rms(its part) * weight * mult, the row cut into ``groups`` equal parts with a root mean square
+    each.  y, z float32 [T, width] (row strides free), out [T, width] in its own dtype (row stride free)."""
+    _dev(y, z, weight, out)
+    T, width = y.shape
+    assert y.dtype == torch.float32 and z.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1 and out.stride(1) == 1
+    assert weight.is_contiguous() and weight.numel() == width and tuple(out.shape) == (T, width)
+    _check(lib().aien_gate_group_norm(_p(y), y.stride(0), _p(z), z.stride(0), _p(weight), dt(weight), float(eps), float(mult), _p(out), dt(out),
+                                      out.stride(0), T, width, int(groups), _stream()), "gate_group_norm")
+
+
+# ---------------------------------------------------------------------------- layers with a scale per channel on each branch
+def scaled_add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], vec: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                       weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor]) -> None:
+    """x += vec * (delta + bias) in float32 (delta [T,H] or partial products [P,T,H]; vec, bias float32 [H] or None), then
+    out = rmsnorm(x) * weight when ``out`` is given."""
+    _dev(x, delta, vec, bias, weight, out)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    for v in (vec, bias):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == H)
+    assert out is None or (out.is_contiguous() and out.shape == x.shape and weight is not None and weight.is_contiguous() and weight.numel() == H)
+    nparts, stride = _parts_of(delta, x.shape)
+    _check(lib().aien_scaled_add_rmsnorm(_p(x), _p(delta), dt(delta) if delta is not None else F32, nparts, stride, _p(vec), _p(bias),
+                                         _p(weight), dt(weight) if weight is not None else F32, float(eps), _p(out),
+                                         dt(out) if out is not None else F32, T, H, _stream()), "scaled_add_rmsnorm")
+
+
+def pass_input(x: torch.Tensor, again: Optional[torch.Tensor], row: torch.Tensor) -> None:
+    """x += again (float32 [T,H], when given), then x += row ([H]) for every token."""
+    _dev(x, again, row)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and row.is_contiguous() and row.numel() == H
+    assert again is None or (again.dtype == torch.float32 and again.is_contiguous() and again.shape == x.shape)
+    _check(lib().aien_pass_input(_p(x), _p(again), _p(row), dt(row), T, H, _stream()), "pass_input")
+
+
+def clamped_glu(a: torch.Tensor, gate_off: int, up_off: int, F_: int, bias_gate: Optional[torch.Tensor], bias_up: Optional[torch.Tensor],
+                limit: float, alpha: float, out: torch.Tensor) -> None:
+    """g = min(a[:, gate_off:][:F] + bias_gate, limit); u = clamp(a[:, up_off:][:F] + bias_up, -limit, limit);
+    out = g * sigmoid(alpha * g) * (u + 1)."""
+    _dev(a, bias_gate, bias_up, out)
+    T = a.shape[0]
+    assert a.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (T, F_)
+    bdt = F32
+    for b in (bias_gate, bias_up):
+        if b is not None:
+            assert b.is_contiguous() and b.numel() == F_
+            bdt = dt(b)
+    assert bias_gate is None or bias_up is None or bias_gate.dtype == bias_up.dtype
+    _check(lib().aien_clamped_glu(_p(a), dt(a), a.stride(0), int(gate_off), int(up_off), _p(bias_gate), _p(bias_up), bdt, float(limit),
+                                  float(alpha), _p(out), dt(out), out.stride(0), T, int(F_), _stream()), "clamped_glu")
+
+
+def sigmoid_gate(o: torch.Tensor, g: Optional[torch.Tensor], mult: float, out: torch.Tensor) -> None:
+    """out = o * sigmoid(g) * mult element by element; o [T, C], g float32 [T, C] or None (no gate), out [T, C]; row strides free."""
+    _dev(o, g, out)
+    T, C = o.shape
+    assert o.stride(1) == 1 and out.stride(1) == 1 and tuple(out.shape) == (T, C)
+    assert g is None or (g.dtype == torch.float32 and g.stride(1) == 1 and tuple(g.shape) == (T, C))
+    _check(lib().aien_sigmoid_gate(_p(o), dt(o), o.stride(0), _p(g), g.stride(0) if g is not None else 0, float(mult), _p(out), dt(out),
+                                   out.stride(0), T, C, _stream()), "sigmoid_gate")
+
+
+def scale_rows(o: torch.Tensor, mult: float, out: torch.Tensor) -> None:
+    """out = o * mult (row strides free)."""
+    sigmoid_gate(o, None, mult, out)
+
+
+# ---------------------------------------------------------------------------- attention with a capped score
+def capped_attention_workspace_bytes(lim, num_heads: int, value_dim: int) -> int:
+    """Scratch of :func:`capped_attention` for the largest step."""
+    return biased_attention_workspace_bytes(lim, num_heads, value_dim, 0)
+
+
+def capped_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor, num_q_heads: int,
+                     num_kv_heads: int, head_dim: int, value_dim: int, window: int, scale: float, softcap: float) -> None:
+    """Causal attention of the step's tokens over one cache group with the scaled score s turned into softcap * tanh(s /
+    softcap) (softcap 0: left as it is), an optional window, values of size ``value_dim``."""
+    k2 = k_cache.view(-1, num_kv_heads, head_dim)
+    v2 = v_cache.view(-1, num_kv_heads, value_dim)
+    paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
+                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim, softcap=softcap)
+
+
+def routed_combine(parts: torch.Tensor, h: Optional[torch.Tensor], w_same: Optional[torch.Tensor], shared: Optional[torch.Tensor],
+                   zs: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = sum_p parts[p] + w_same[t] * h[t] + sigmoid(zs[t]) * shared[t] (float32 [T,H]).  parts [P,T,H]; ``h`` with
+    ``w_same`` float32 [T] or neither; ``shared`` [T,H] or partial products [Q,T,H], or None; ``zs`` float32 [T] (stride free)
+    or None (the shared term then counts whole)."""
+    _dev(parts, h, w_same, shared, zs, out)
+    P_, T, H = parts.shape
+    assert parts.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, H)
+    assert (h is None) == (w_same is None)
+    if h is not None:
+        assert h.stride(1) == 1 and w_same.dtype == torch.float32 and w_same.is_contiguous() and w_same.numel() >= T
+    sparts, sstride = _parts_of(shared, (T, H))
+    assert zs is None or zs.dtype == torch.float32
+    _check(lib().aien_routed_combine(_p(parts), dt(parts), P_, T * H, _p(h), dt(h) if h is not None else F32, h.stride(0) if h is not None else 0,
+                                     _p(w_same), _p(shared), dt(shared) if shared is not None else F32, sparts, sstride, _p(zs),
+                                     zs.stride(0) if zs is not None else 0, _p(out), T, H, _stream()), "routed_combine")
+
+
+def moe_route_biased(z: torch.Tensor, num_experts: int, real: int, top: int, renorm: bool, renorm_eps: float,
+                     correction: Optional[torch.Tensor], ids: torch.Tensor, wts: torch.Tensor, w_same: Optional[torch.Tensor],
+                     expert_count: Optional[torch.Tensor] = None) -> None:
+    """Router with a correction on the choice: s = softmax(z[:, :num_experts]) (float32); the ``top`` largest s + correction
+    are chosen; weights s (``renorm``: divided by their sum + renorm_eps).  Experts from ``real`` on return their input:
+    their weights are summed into ``w_same`` [T] and their choices handed on as expert 0 with weight zero."""
+    _dev(z, correction, ids, wts, w_same, expert_count)
+    T = z.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= num_experts and ids.dtype == torch.int32 and wts.dtype == torch.float32
+    assert ids.is_contiguous() and wts.is_contiguous() and ids.numel() >= T * top and wts.numel() >= T * top
+    assert correction is None or (correction.is_contiguous() and correction.numel() == num_experts)
+    assert w_same is None or (w_same.dtype == torch.float32 and w_same.is_contiguous() and w_same.numel() >= T)
+    _check(lib().aien_moe_route_biased(_p(z), z.stride(0), T, int(num_experts), int(real), int(top), 1 if renorm else 0, float(renorm_eps),
+                                       _p(correction), dt(correction) if correction is not None else F32, _p(ids), _p(wts), _p(w_same),
+                                       _p(expert_count), _stream()), "moe_route_biased")
+
+
+def rope_halves_value_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nq: int, nkv: int, hd: int, hdv: int,
+                            cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, slot_map: torch.Tensor,
+                            q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """q, k (heads of ``hd``) and v (heads of ``hdv``) are column blocks of the float32 rows ``proj``; the first ``rot``
+    dimensions of every q and k head turn (i with i + rot/2) by cos/sin float32 [T, rot/2]; q goes to ``q_out`` [T, nq*hd],
+    k and v to the token's cache slot (k_cache [slots, nkv, hd], v_cache [slots, nkv, hdv])."""
+    _dev(proj, cos, sin, slot_map, q_out, k_cache, v_cache)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.dtype == v_cache.dtype and slot_map.dtype == torch.int32
+    if rot:
+        assert cos is not None and tuple(cos.shape) == (T, rot // 2) and cos.is_contiguous() and sin.is_contiguous()
+    _check(lib().aien_rope_halves_value_write(_p(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), int(nq), int(nkv), int(hd), int(hdv),
+                                              _p(cos), _p(sin), int(rot), _p(slot_map), _p(q_out), dt(q_out), q_out.stride(0), _p(k_cache),
+                                              _p(v_cache), dt(k_cache), T, _stream()), "rope_halves_value_write")

@@ -1,4 +1,4 @@
-from . import llama_qwen3, dulisun, ripesun, botalorn  # noqa: F401  (registers the architectures)
+from . import llama_qwen3, dulisun, ripesun, botalorn, mumazen  # noqa: F401  (registers the architectures)
 from .decoder import Decoder
 from .loading import build_model_from_folder, build_model_from_config, model_spec_for
 

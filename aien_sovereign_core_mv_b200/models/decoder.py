@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..config.spec import LayerSpec, ModelSpec, PartSpec
-from ..parts.base import Prenormed, Block, CacheNeed, Mixer, NormedStream, RunBinding, StepContext, StreamCopy
+from ..parts.base import Prenormed, Block, CacheNeed, Mixer, NormedStream, RunBinding, ScaledSum, StepContext, StreamCopy, add_to_residual
 from ..registry import make_part, part_factory
 
 
@@ -42,6 +42,13 @@ class Decoder:
         # the parts outside the layers, with the spec entry that names their tensors
         self._ends = {"embedding": (self.embedding, spec.embedding), "final_norm": (self.final_norm, spec.final_norm),
                       "head": (self.head, spec.head)}
+        # what a repeated stretch of layers adds to the stream before each of its passes
+        self.pass_input = None
+        if spec.pass_input is not None:
+            if spec.streams > 1:
+                raise ValueError("a pass input is defined for models with one residual stream")
+            self.pass_input = make_part("pass_input", spec.pass_input.kind, hidden_size=spec.hidden_size, **own(spec.pass_input))
+            self._ends["pass_input"] = (self.pass_input, spec.pass_input)
         # ---- cache groups: runs with equal needs share pools and block tables
         self.group_needs: List[CacheNeed] = []
         self.group_slots: List[int] = []          # planes (cache slots) per group
@@ -114,6 +121,8 @@ class Decoder:
     def parts(self):
         """Every part of the model, for whoever must ask all of them something."""
         out = [self.embedding, self.final_norm, self.head] + list(self._positions.values())
+        if self.pass_input is not None:
+            out.append(self.pass_input)
         for block in self.blocks:
             out.append(block)
             out.extend(block.parts().values())
@@ -195,6 +204,8 @@ class Decoder:
 
     def step_workspace_bytes(self, lim) -> int:
         n = self.streams * lim.max_tokens * self.hidden_size * 4 + 4096
+        if self.pass_input is not None:
+            n += lim.max_tokens * self.hidden_size * 4 + 256          # the embedding's output, kept for the later passes
         for p in self._positions.values():
             if hasattr(p, "step_workspace_bytes"):
                 n += p.step_workspace_bytes(lim.max_tokens)
@@ -214,9 +225,17 @@ class Decoder:
             self.embedding.forward(ctx, ctx.token_ids, x)
         delta = None
         runs = self.spec.run_list
+        x0 = None
+        if self.pass_input is not None and self.pass_input.wants_embedding:
+            x0 = ws.take_step((ctx.num_tokens, self.hidden_size), torch.float32)
+            K.convert(x, x0)
         for i, (run, binding) in enumerate(zip(runs, self.bindings)):
             ws.begin_layer()
             block = self.blocks[run.layer]
+            if run.enter >= 0:
+                add_to_residual(ctx, x, delta)                  # the pass starts from the stream as it stands
+                delta = None
+                self.pass_input.forward(ctx, x, x0, run.enter)
             if block.chains_norm:
                 # the norm that will take this block's result, so that the block's last product may work for it
                 nxt = self.blocks[runs[i + 1].layer].first_norm() if i + 1 < len(runs) else None
@@ -225,6 +244,9 @@ class Decoder:
                 delta = block.forward(ctx, x, delta, binding)
         ws.end_layers()
         if isinstance(delta, (Prenormed, StreamCopy, NormedStream)):    # nothing is pending: the last block summed into the stream itself
+            delta = None
+        if isinstance(delta, ScaledSum):                                # a pending sum that the row gather cannot take
+            add_to_residual(ctx, x, delta)
             delta = None
         if num_rows > 0:
             rows = ws.take((num_rows, self.hidden_size), torch.float32)

@@ -1,6 +1,6 @@
 from .base import (Block, CacheNeed, Embedding, FeedForward, GroupView, Head, Mixer, Norm, Part, Position, RunBinding,
                    StepContext, StepLimits, Workspace, add_to_residual)
-from . import norm, rotary, attention, chunk_attention, latent_attention, conv_attention, recurrent, mlp, moe, block, sandwich, hyper, ends  # noqa: F401  (registers the built-in parts)
+from . import norm, rotary, state_space, attention, chunk_attention, latent_attention, conv_attention, recurrent, mlp, moe, block, sandwich, hyper, ends  # noqa: F401  (registers the built-in parts)
 from .linear import linear
 
 __all__ = ["Block", "CacheNeed", "Embedding", "FeedForward", "GroupView", "Head", "Mixer", "Norm", "Part", "Position",

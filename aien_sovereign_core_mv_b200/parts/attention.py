@@ -116,3 +116,88 @@ class PagedAttention(Mixer):
         K.paged_attention(ctx, q_out, k_cache, v_cache, group, out, self.num_heads, self.num_kv_heads, self.head_dim,
                           self.window, self.scale)
         return linear_into_residual(ctx, out, self.w_o, sink) or linear(ctx, out, self.w_o, may_defer_sum=True)
+
+
+from .state_space import BranchMixer            # noqa: E402  (the two-products form this mixer follows)
+
+
+@register_mixer("gated_capped_attention")
+class GatedCappedAttention(BranchMixer):
+    """Grouped-query attention with a capped score and an output gate.  q = W_q h (``num_heads`` heads of ``head_dim``),
+    k = W_k h, v = W_v h (``num_kv_heads`` heads; values of ``value_dim`` numbers), no biases; q and k are rotated over the
+    dimensions the position part names (halves: i with i + d/2; the rest pass unchanged); score = q.k * ``scale``, then
+    (``softcap`` c > 0) c * tanh(score / c); causal, optionally only the last ``window`` keys; ordinary softmax.  The
+    concatenated heads are multiplied element by element by sigmoid(W_g h) (``gate``) and projected by W_o.  One product
+    makes q | k | v | g.  Rotation, scores, softmax and the gate are float32 in both engine precisions."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: Position,
+                 value_dim: Optional[int] = None, scale: Optional[float] = None, softcap: float = 0.0, window: int = 0, gate: bool = True):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.value_dim = int(value_dim if value_dim is not None else head_dim)
+        if not (0 < self.head_dim <= 256 and 0 < self.value_dim <= 256):
+            raise ValueError(f"head sizes {self.head_dim} / {self.value_dim}: the attention kernels take sizes up to 256")
+        if getattr(position, "pairing", "halves") != "halves":
+            raise ValueError("this mixer rotates halves (i with i + d/2)")
+        self.position = position
+        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        self.softcap, self.window, self.gate = float(softcap or 0.0), int(window or 0), bool(gate)
+        if self.softcap < 0.0 or self.window < 0:
+            raise ValueError("softcap and window must not be negative")
+        self.q_dim, self.k_dim, self.v_dim = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, self.num_kv_heads * self.value_dim
+        self.out_cols = self.num_heads * self.value_dim
+        self.in_rows = self.q_dim + self.k_dim + self.v_dim + (self.out_cols if self.gate else 0)
+        self.w_in = self.w_o = None
+
+    def param_shapes(self):
+        H = self.hidden_size
+        shapes = {"q_proj": ((self.q_dim, H), "matrix"), "k_proj": ((self.k_dim, H), "matrix"), "v_proj": ((self.v_dim, H), "matrix"),
+                  "o_proj": ((H, self.out_cols), "matrix")}
+        if self.gate:
+            shapes["g_proj"] = ((self.out_cols, H), "matrix")
+        return shapes
+
+    def bind(self, tensors):
+        rows = [tensors[n] for n in ("q_proj", "k_proj", "v_proj")] + ([tensors["g_proj"]] if self.gate else [])
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.w_in = torch.cat(rows, dim=0).contiguous()                 # rows q | k | v | g
+        self.w_o = tensors["o_proj"].contiguous()
+
+    def in_weight(self):
+        return self.w_in
+
+    def out_weight(self):
+        return self.w_o
+
+    def cache_need(self):
+        planes = (("k", (self.num_kv_heads, self.head_dim)), ("v", (self.num_kv_heads, self.value_dim)))
+        return CacheNeed("window" if self.window > 0 else "full", self.window, planes)
+
+    def store(self, ctx, run):
+        group = ctx.groups[run.group]
+        return group, group.storage["k"][run.slot], group.storage["v"][run.slot]
+
+    def core_workspace_bytes(self, lim):
+        return lim.max_tokens * (self.q_dim + self.out_cols) * lim.itemsize + 1024 \
+            + K.capped_attention_workspace_bytes(lim, self.num_heads, self.value_dim)
+
+    def core(self, ctx, proj, col0, store, out, out_col0, mult):
+        T = ctx.num_tokens
+        group, k_cache, v_cache = store
+        rot = self.position.rotary(ctx)
+        cos, sin, rdim = rot if rot is not None else (None, None, 0)
+        q = ctx.workspace.take((T, self.q_dim), ctx.dtype)
+        K.rope_halves_value_write(proj, col0, col0 + self.q_dim, col0 + self.q_dim + self.k_dim, self.num_heads, self.num_kv_heads,
+                                  self.head_dim, self.value_dim, cos, sin, rdim, group.slot_map, q, k_cache, v_cache)
+        dst = out[:, out_col0:out_col0 + self.out_cols]
+        gated = self.gate or mult != 1.0
+        o = ctx.workspace.take((T, self.out_cols), ctx.dtype) if gated else dst
+        K.capped_attention(ctx, q, k_cache, v_cache, group, o, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
+                           self.window, self.scale, self.softcap)
+        if self.gate:
+            g0 = col0 + self.q_dim + self.k_dim + self.v_dim
+            K.sigmoid_gate(o, proj[:, g0:g0 + self.out_cols], mult, dst)
+        elif gated:
+            K.scale_rows(o, mult, dst)

@@ -239,6 +239,18 @@ class NormedStream:
 
 
 @dataclass
+class ScaledSum:
+    """What a block with a scale per channel on its branches hands on: ``vec * (delta + bias)`` is still to be added to
+    the stream (``delta`` a [T, H] tensor or float32 partial products [P, T, H]; ``vec`` and ``bias`` float32 [H] or
+    None).  The next block of that kind adds it inside its first norm's kernel; every other consumer calls
+    ``add_to_residual``."""
+
+    delta: torch.Tensor
+    vec: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+
+
+@dataclass
 class ResidualSink:
     """Offered to a part whose last product ends a residual branch: instead of returning the
     branch's output for the next norm to add, the product may add it to ``x`` itself and return a
@@ -320,6 +332,11 @@ class FeedForward(Part):
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def pending_bias(self) -> Optional[torch.Tensor]:
+        """A float32 vector [H] that belongs to the result of forward() and that the consumer of the branch adds with
+        the sum (the bias of the last product), for blocks that can take it (``ScaledSum``); None: there is none."""
+        return None
+
 
 class Embedding(Part):
     """Token ids to the float32 residual stream."""
@@ -353,6 +370,9 @@ def add_to_residual(ctx: StepContext, x: torch.Tensor, delta) -> None:
     not fuse the residual sum into a norm."""
     from .. import kernels as K
     if delta is None or isinstance(delta, (Prenormed, StreamCopy, NormedStream)):
+        return
+    if isinstance(delta, ScaledSum):
+        K.scaled_add_rmsnorm(x, delta.delta, delta.vec, delta.bias, None, 0.0, None)
         return
     K.add_residual(x, delta)
 

@@ -6,8 +6,8 @@ from typing import Optional
 import torch
 
 from .. import kernels as K
-from ..registry import make_part, register_embedding, register_head
-from .base import Embedding, Head, StepContext
+from ..registry import make_part, register_embedding, register_head, register_pass_input
+from .base import Embedding, Head, Part, StepContext
 from .linear import linear
 
 
@@ -120,3 +120,32 @@ class LinearHead(Head):
         linear(ctx, rows, self.weight, out=logits)
         if self.softcap > 0.0:
             K.softcap(logits, self.softcap)
+
+
+@register_pass_input("step_vector")
+class StepVectorInput(Part):
+    """What a stretch of layers that runs ``times`` times in a row adds to the stream before pass t = 0, 1, ...: the
+    embedding's output once more (``add_embedding``; every pass but the first), then the row t of ``steps`` [times,
+    hidden] for every token.  The sums are float32."""
+
+    def __init__(self, hidden_size: int, times: int, add_embedding: bool = True):
+        self.hidden_size, self.times, self.add_embedding = int(hidden_size), int(times), bool(add_embedding)
+        if self.times <= 0:
+            raise ValueError(f"times {times!r} must be positive")
+        self.steps: Optional[torch.Tensor] = None
+
+    @property
+    def wants_embedding(self) -> bool:
+        """Whether the decoder keeps the embedding's output for this part."""
+        return self.add_embedding and self.times > 1
+
+    def param_shapes(self):
+        return {"steps": ((self.times, self.hidden_size), "small")}
+
+    def bind(self, tensors):
+        self.steps = tensors["steps"].contiguous()
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, embedded: Optional[torch.Tensor], t: int) -> None:
+        if not (0 <= t < self.times):
+            raise ValueError(f"pass {t} of {self.times}")
+        K.pass_input(x, embedded if (self.add_embedding and t > 0) else None, self.steps[t])

@@ -89,3 +89,48 @@ class ActMLP(FeedForward):
     def forward(self, ctx: StepContext, h: torch.Tensor):
         a = linear(ctx, h, self.w_up, act=self.act)
         return linear(ctx, a, self.w_down, out_dtype=torch.float32, may_defer_sum=True)    # the branch norm adds partial products
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """g = min(W_gate h + b_gate, ``limit``), u = clamp(W_up h + b_up, -limit, limit); y = W_down (g * sigmoid(``alpha`` g)
+    * (u + 1)) + b_down.  One product makes gate | up; its float32 result, the biases and the activation meet in one
+    kernel.  The last bias is handed to the consumer of the branch (``pending_bias``), which adds it with the sum."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, bias: bool = True):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha, self.bias = float(limit), float(alpha), bool(bias)
+        if not self.limit > 0.0:
+            raise ValueError(f"limit {limit!r} must be positive")
+        self.w_gate_up = self.w_down = self.b_gate = self.b_up = self.b_down = None
+
+    def param_shapes(self):
+        H, I = self.hidden_size, self.intermediate_size
+        shapes = {"gate": ((I, H), "matrix"), "up": ((I, H), "matrix"), "down": ((H, I), "matrix")}
+        if self.bias:
+            shapes.update({"gate_bias": ((I,), "small"), "up_bias": ((I,), "small"), "down_bias": ((H,), "small")})
+        return shapes
+
+    def bind(self, tensors):
+        g, u = tensors["gate"], tensors["up"]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()           # rows gate | up
+        self.w_down = tensors["down"].contiguous()
+        if self.bias:
+            self.b_gate, self.b_up = tensors["gate_bias"].float().contiguous(), tensors["up_bias"].float().contiguous()
+            self.b_down = tensors["down_bias"].float().contiguous()
+
+    def workspace_bytes(self, lim):
+        I = self.intermediate_size
+        return lim.max_tokens * (2 * I * 4 + I * lim.itemsize + self.hidden_size * 4) + 8192 + K.PARTIALS_MAX_BYTES
+
+    def pending_bias(self):
+        return self.b_down
+
+    def forward(self, ctx: StepContext, h: torch.Tensor):
+        I = self.intermediate_size
+        gu = linear(ctx, h, self.w_gate_up, out_dtype=torch.float32)
+        act = ctx.workspace.take((ctx.num_tokens, I), ctx.dtype)
+        K.clamped_glu(gu, 0, I, I, self.b_gate, self.b_up, self.limit, self.alpha, act)
+        return linear(ctx, act, self.w_down, out_dtype=torch.float32, may_defer_sum=True)

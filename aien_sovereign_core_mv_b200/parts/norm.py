@@ -7,7 +7,7 @@ import torch
 
 from .. import kernels as K
 from ..registry import register_norm
-from .base import Norm, NormedStream, Prenormed, ResidualSink, StepContext, StreamCopy
+from .base import Norm, NormedStream, Prenormed, ResidualSink, ScaledSum, StepContext, StreamCopy, add_to_residual
 
 # AIEN_B200_FUSED_NORM=0 keeps every norm in its own kernel
 _FUSE = __import__("os").environ.get("AIEN_B200_FUSED_NORM", "1").strip() not in ("0", "off", "no")
@@ -89,6 +89,9 @@ class RMSNorm(Norm):
             delta = None
         if isinstance(delta, StreamCopy):
             delta = None                          # nothing pending
+        if isinstance(delta, ScaledSum):
+            add_to_residual(ctx, x, delta)        # left by a block that scales its branches
+            delta = None
         out = ctx.workspace.take(tuple(x.shape), ctx.dtype)
         K.add_rmsnorm(x, delta, self.weight, self.eps, out)
         return out

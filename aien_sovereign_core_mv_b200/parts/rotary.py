@@ -12,7 +12,7 @@ from .base import Position, StepContext
 
 
 def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None,
-                        theta_as_float32: bool = True):
+                        theta_as_float32: bool = True, linear_factor: float = 1.0):
     """inv_freq_i = theta^(-2i/d) in float64 (theta itself held as float32, as the reference
     does, unless ``theta_as_float32`` is off), optionally smoothed the llama3 way
     (crates/aien-abi-core/src/lib.rs:69-84, 106-114)."""
@@ -34,6 +34,8 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[dict] = N
                 smooth = (old / wavelen - scaling["low_freq_factor"]) / (scaling["high_freq_factor"] - scaling["low_freq_factor"])
                 out.append((1.0 - smooth) * f / scaling["factor"] + smooth * f)
         inv = out
+    if linear_factor and float(linear_factor) != 1.0:
+        inv = [f / float(linear_factor) for f in inv]          # linear scaling: every frequency divided by one factor
     return inv
 
 
@@ -43,10 +45,10 @@ class RotaryPosition(Position):
     (crates/aien-inference-abi/src/tensor.rs:150-188).  The table of a step is built once and
     shared by every layer that uses the same part.  ``pairing`` says which dimensions a mixer
     rotates together: "halves" (i with i + d/2, rotate_half) or "interleaved" (2i with 2i+1); the
-    table is the same, the mixer's kernel reads ``pairing``."""
+    table is the same, the mixer's kernel reads ``pairing``.  ``linear_factor`` f: every frequency is divided by f."""
 
     def __init__(self, head_dim: int, theta: float, scaling: Optional[dict] = None, rotary_dim: Optional[int] = None,
-                 pairing: str = "halves", theta_as_float32: bool = True):
+                 pairing: str = "halves", theta_as_float32: bool = True, linear_factor: float = 1.0):
         if pairing not in ("halves", "interleaved"):
             raise ValueError(f"rotary pairing {pairing!r}: 'halves' or 'interleaved'")
         self.pairing = pairing
@@ -56,7 +58,10 @@ class RotaryPosition(Position):
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self.theta = float(theta)
         self.scaling = dict(scaling) if scaling else None
-        self._inv_host = inverse_frequencies(self.head_dim, self.theta, self.scaling, self.rotary_dim, bool(theta_as_float32))
+        self.linear_factor = float(linear_factor or 1.0)
+        if self.linear_factor <= 0.0:
+            raise ValueError(f"linear_factor {linear_factor!r} must be positive")
+        self._inv_host = inverse_frequencies(self.head_dim, self.theta, self.scaling, self.rotary_dim, bool(theta_as_float32), self.linear_factor)
         self._inv_dev: Optional[torch.Tensor] = None
 
     def step_workspace_bytes(self, max_tokens):

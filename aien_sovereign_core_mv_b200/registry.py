@@ -11,7 +11,7 @@ from typing import Any, Callable, Dict
 
 _ARCHITECTURES: Dict[str, Callable[..., Any]] = {}
 _PARTS: Dict[str, Dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "side": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "side": {}, "pass_input": {},
 }
 
 
@@ -78,6 +78,11 @@ def register_head(kind: str):
 def register_side(kind: str):
     """A per-layer input besides the residual stream (e.g. a second embedding of the token)."""
     return _register("side", kind)
+
+
+def register_pass_input(kind: str):
+    """What is added to the residual stream before a pass of a repeated run of layers."""
+    return _register("pass_input", kind)
 
 
 def part_factory(family: str, kind: str):

@@ -29,7 +29,9 @@ def random_tensor(name: str, shape: Tuple[int, ...], kind: str, seed: int,
                   init_std: Optional[float] = None, device: str = "cpu") -> torch.Tensor:
     """``kind``: "matrix" ([out, in]), "embedding", "norm" (a vector of scales around one), "norm_offset"
     (a vector of scales stored around zero), "vector" (free numbers of order one, e.g. softmax sinks), "fraction"
-    (numbers in [0, 1), e.g. a mixing weight) or "near_identity" (a square matrix: the identity plus N(0, 0.1))."""
+    (numbers in [0, 1), e.g. a mixing weight), "near_identity" (a square matrix: the identity plus N(0, 0.1)), "small"
+    (N(0, 0.1): biases), "log_rate" (U(-4, 1): logarithms of decay rates) or "rate_bias" (U(-4.5, -1): what a softplus
+    turns into a small step size)."""
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if kind == "norm":
@@ -38,6 +40,12 @@ def random_tensor(name: str, shape: Tuple[int, ...], kind: str, seed: int,
         t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 0.4 - 0.2
     elif kind == "vector":
         t = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
+    elif kind == "small":
+        t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.1
+    elif kind == "log_rate":
+        t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 5.0 - 4.0
+    elif kind == "rate_bias":
+        t = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 3.5 - 4.5
     elif kind == "fraction":
         t = torch.rand(shape, generator=g, device=device, dtype=torch.float32)
     elif kind == "near_identity":
