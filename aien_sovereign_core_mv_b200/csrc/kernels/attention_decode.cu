@@ -267,8 +267,14 @@ paged_decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride
                 const int hq = kvh * G + (h < G ? h : 0);
                 const float sc_h = ht.head_scale != nullptr ? scale * ht.head_scale[hq] : scale;
                 const float sl_h = ht.slopes != nullptr ? ht.slopes[hq] : 0.f;
-                Sc[(warp * 16 + g) * NH + h] = ok0 ? S[nt][e] * sc_h - sl_h * (float)(pos - kj0) : -INFINITY;
-                Sc[(warp * 16 + g + 8) * NH + h] = ok1 ? S[nt][2 + e] * sc_h - sl_h * (float)(pos - kj1) : -INFINITY;
+                float s0 = S[nt][e] * sc_h, s1 = S[nt][2 + e] * sc_h;
+                if (ht.softcap > 0.f) {                          // the cap stands on q.k * scale, ahead of the head's factor
+                    const float hs = ht.head_scale != nullptr ? ht.head_scale[hq] : 1.0f;
+                    s0 = ht.softcap * hs * tanh_ex2(S[nt][e] * scale / ht.softcap);
+                    s1 = ht.softcap * hs * tanh_ex2(S[nt][2 + e] * scale / ht.softcap);
+                }
+                Sc[(warp * 16 + g) * NH + h] = ok0 ? s0 - sl_h * (float)(pos - kj0) : -INFINITY;
+                Sc[(warp * 16 + g + 8) * NH + h] = ok1 ? s1 - sl_h * (float)(pos - kj1) : -INFINITY;
             }
     }
     __syncthreads();
@@ -417,14 +423,14 @@ AIEN_API int aien_paged_attention_decode_masked(
 }
 
 // The plain split-key kernel with terms per query head (see HeadTerms; each pointer may be null): head_scale and
-// slopes are float32 [nq], gate float32 rows of the step's tokens with ldg numbers between rows.
+// slopes are float32 [nq], gate float32 rows of the step's tokens with ldg numbers between rows; softcap 0: none.
 AIEN_API int aien_paged_attention_decode_terms(
     const void* q, long q_stride, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
     const int* seq_of_token, const int* positions, const int* token_list, void* out, long out_stride, float* part_out,
     float* part_ml, int* counters, int nq, int nkv, int hd, int page_size, int window, float scale, int max_splits, int T,
-    const float* head_scale, const float* slopes, const float* gate, long ldg, cudaStream_t stream) {
+    const float* head_scale, const float* slopes, const float* gate, long ldg, float softcap, cudaStream_t stream) {
     FusedQK none = {};
-    const HeadTerms ht{head_scale, slopes, gate, ldg};
+    const HeadTerms ht{head_scale, slopes, gate, ldg, softcap > 0.f ? softcap : 0.f};
     return decode_dispatch(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_of_token, positions, token_list, out,
                            out_stride, part_out, part_ml, counters, nq, nkv, hd, page_size, window, scale, max_splits, T, none, stream,
                            0, nullptr, ht);

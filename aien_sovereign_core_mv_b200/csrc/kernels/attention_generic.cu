@@ -61,8 +61,16 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
             if (page >= 0) {
                 slot = page * page_size + (j % page_size);
                 const TKV* kp = k_cache + ((size_t)slot * nkv + kvh) * hd;
-                float dot = 0.f;
-                for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f(kp[d]), dot);
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;       // four chains: a quarter of the rounding error's growth
+                int d = 0;
+                for (; d + 3 < hd; d += 4) {
+                    d0 = fmaf(qs[d], to_f(kp[d]), d0);
+                    d1 = fmaf(qs[d + 1], to_f(kp[d + 1]), d1);
+                    d2 = fmaf(qs[d + 2], to_f(kp[d + 2]), d2);
+                    d3 = fmaf(qs[d + 3], to_f(kp[d + 3]), d3);
+                }
+                for (; d < hd; ++d) d0 = fmaf(qs[d], to_f(kp[d]), d0);
+                const float dot = (d0 + d1) + (d2 + d3);
                 score = dot * scale;
                 if (softcap > 0.f) score = softcap * tanhf(score / softcap);
                 if (head_scale) score *= hscale;
@@ -78,17 +86,18 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, long q_stride,
         const float csum = block_sum(e, red);           // also orders the writes to p/slots
         const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
         l = l * corr + csum;
-        acc0 *= corr;
-        acc1 *= corr;
         const int n = (pos - base + 1 < AG_THREADS) ? pos - base + 1 : AG_THREADS;
+        float part0 = 0.f, part1 = 0.f;                   // the chunk's own sum, added to the running one at its end
         for (int jj = 0; jj < n; ++jj) {
             const int sl = slots[jj];
             if (sl < 0) continue;
             const float pj = p[jj];
             const TKV* vp = v_cache + ((size_t)sl * nkv + kvh) * hdv;
-            if (tid < hdv) acc0 = fmaf(pj, to_f(vp[tid]), acc0);
-            if (tid + AG_THREADS < hdv) acc1 = fmaf(pj, to_f(vp[tid + AG_THREADS]), acc1);
+            if (tid < hdv) part0 = fmaf(pj, to_f(vp[tid]), part0);
+            if (tid + AG_THREADS < hdv) part1 = fmaf(pj, to_f(vp[tid + AG_THREADS]), part1);
         }
+        acc0 = fmaf(acc0, corr, part0);
+        acc1 = fmaf(acc1, corr, part1);
         m = m_new;
         __syncthreads();
     }

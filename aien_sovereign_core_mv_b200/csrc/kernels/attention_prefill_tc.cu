@@ -326,7 +326,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         float m_ref = -INFINITY, l_run = 0.f;
         // terms per head: the score in log2 units becomes s * (scale * head_scale[h]) - slope[h] * (hi - key), made
         // in place before the limits of the row are applied; the maximum and the exponentials then take it as it is
-        const bool terms = ht.head_scale != nullptr || ht.slopes != nullptr;
+        const bool terms = ht.head_scale != nullptr || ht.slopes != nullptr || ht.softcap > 0.f;
+        // a capped score: c * tanh(s * scale / c), in log2 units, times the head's factor
+        const float cap_in = ht.softcap > 0.f ? scale_log2e * 0.6931471805599453f / ht.softcap : 0.f;
+        const float cap_l2 = ht.softcap * 1.4426950408889634f * (ht.head_scale != nullptr ? ht.head_scale[head_a + h] : 1.0f);
         const float hs_l2 = scale_log2e * (ht.head_scale != nullptr ? ht.head_scale[head_a + h] : 1.0f);
         const float slope_l2 = ht.slopes != nullptr ? ht.slopes[head_a + h] * 1.4426950408889634f : 0.f;
         const float sl = terms ? 1.0f : scale_log2e;
@@ -344,7 +347,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (terms) {
                 const float at0 = -slope_l2 * (float)(hi - key_base);            // the bias of the block's first key
 #pragma unroll
-                for (int i = 0; i < PT_BN; ++i) v[i] = __float_as_uint(fmaf(__uint_as_float(v[i]), hs_l2, fmaf((float)i, slope_l2, at0)));
+                for (int i = 0; i < PT_BN; ++i) {
+                    const float raw = __uint_as_float(v[i]), bias = fmaf((float)i, slope_l2, at0);
+                    v[i] = __float_as_uint(ht.softcap > 0.f ? fmaf(tanh_ex2(raw * cap_in), cap_l2, bias) : fmaf(raw, hs_l2, bias));
+                }
             }
             if (key_base + PT_BN - 1 > hi) {                                     // the block on the diagonal: columns beyond hi
                 const int last = hi - key_base;
@@ -618,14 +624,15 @@ AIEN_API int aien_paged_attention_prefill_tc_supports(int hd, int page_size) {
 // force_splits: 0 lets the launch choose, n > 0 asks for n ranges (refused if the scratch is too small).
 // chunk > 0: a query sees only the keys of its own chunk of that many positions; sinks (float32 [nq], may be null):
 // one more term exp(sink) in every head's softmax denominator.  With either, every tile's keys stay in one range.
-// head_scale, slopes (float32 [nq]) and gate (float32 [tokens of the step, ldg]), each of which may be null: see HeadTerms.
+// head_scale, slopes (float32 [nq]) and gate (float32 [tokens of the step, ldg]), each of which may be null, and softcap
+// (0: none): see HeadTerms.
 AIEN_API int aien_paged_attention_prefill_tc_terms(
     const void* q, long q_stride, int q_rows, const void* k_cache, const void* v_cache, int cache_rows, const int* block_table,
     int max_blocks, const int* q_start, const int* ctx_len, const int* tile_seq, const int* tile_q0, int num_tiles, void* out,
     long out_stride, int nq, int nkv, int hd, int page_size, int window, float scale, void* scratch, long scratch_bytes, int max_ctx,
     int force_splits, int chunk, const float* sinks, const float* head_scale, const float* slopes, const float* gate, long ldg,
-    cudaStream_t stream) {
-    const HeadTerms ht{head_scale, slopes, gate, ldg};
+    float softcap, cudaStream_t stream) {
+    const HeadTerms ht{head_scale, slopes, gate, ldg, softcap > 0.f ? softcap : 0.f};
     if (num_tiles <= 0) return 0;
     if (chunk < 0) return AIEN_E_SHAPE;
     if (!aien_paged_attention_prefill_tc_supports(hd, page_size) || nkv <= 0 || nq % nkv != 0 || q_rows <= 0 || cache_rows <= 0)
@@ -666,7 +673,7 @@ AIEN_API int aien_paged_attention_prefill_tc_masked(
     int force_splits, int chunk, const float* sinks, cudaStream_t stream) {
     return aien_paged_attention_prefill_tc_terms(q, q_stride, q_rows, k_cache, v_cache, cache_rows, block_table, max_blocks, q_start, ctx_len,
                                                  tile_seq, tile_q0, num_tiles, out, out_stride, nq, nkv, hd, page_size, window, scale,
-                                                 scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, nullptr, nullptr, nullptr, 0, stream);
+                                                 scratch, scratch_bytes, max_ctx, force_splits, chunk, sinks, nullptr, nullptr, nullptr, 0, 0.f, stream);
 }
 
 AIEN_API int aien_paged_attention_prefill_tc_split(

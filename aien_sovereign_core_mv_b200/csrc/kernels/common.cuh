@@ -23,12 +23,14 @@
 
 // Terms per query head that an attention kernel may be given beside the scaled score q.k * scale (any may be null):
 // head_scale[h] multiplies it; slopes[h] * (query position - key position) is taken off it; the head's output is
-// multiplied by sigmoid(gate[t * ldg + h]) (float32 rows of the step's tokens).
+// multiplied by sigmoid(gate[t * ldg + h]) (float32 rows of the step's tokens).  softcap c > 0: the scaled score s
+// becomes c * tanh(s / c) before the other terms.
 struct HeadTerms {
     const float* head_scale;
     const float* slopes;
     const float* gate;
     long ldg;
+    float softcap;
 };
 
 namespace aien {
@@ -45,6 +47,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 __device__ __forceinline__ float load_dyn(const void* p, int dt, size_t i) {
     return dt == AIEN_DT_F32 ? reinterpret_cast<const float*>(p)[i]
                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// tanh from one exponential and one reciprocal of the special-function unit: 1 - 2 / (e^(2x) + 1); the absolute error
+// stays near 1e-7 over the whole range (for large x the quotient underflows to 0 and the result is 1).
+__device__ __forceinline__ float tanh_ex2(float x) {
+    float t;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(x * 2.8853900817779268f));
+    return 1.0f - __fdividef(2.0f, t + 1.0f);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -1,9 +1,10 @@
 // C[M,N] = A[M,K] . W[N,K]^T with float32 accumulation on the CUDA cores.
 //
 // This is the engine's true-32-bit matrix product (no tensor-core mode of any kind) and the
-// plain product every faster kernel is checked against.  Each output element is one chain of
-// fused multiply-adds over k = 0..K-1 in order, so a row's result depends on that row and W
-// only: not on M, not on where the row sits in the batch.  Any M, N, K, any leading
+// plain product every faster kernel is checked against.  Each output element is a chain of
+// fused multiply-adds over every block of 16 values of k in order, the blocks' sums added in
+// order (the rounding error then grows with K/16 + 16 rather than with K), so a row's result
+// depends on that row and W only: not on M, not on where the row sits in the batch.  Any M, N, K, any leading
 // dimensions.  W is the checkpoint's own [out, in] row-major layout (the reference's
 // matmul_vec convention, crates/aien-inference-abi/src/tensor.rs:22-61).
 #include "common.cuh"
@@ -37,6 +38,11 @@ gemm_simple_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W,
             Ws[c][r] = (gn < N && gk < K) ? to_f(W[(size_t)gn * ldw + gk]) : 0.f;
         }
         __syncthreads();
+        float blk[4][4];                                  // the block's own sum, added to the running one at its end
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) blk[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < GS_BK; ++kk) {
             float a[4], b[4];
@@ -47,8 +53,12 @@ gemm_simple_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W,
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) blk[i][j] = fmaf(a[i], b[j], blk[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += blk[i][j];
         __syncthreads();
     }
 #pragma unroll

@@ -154,8 +154,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_paged_attention_prefill_tc_masked": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P],
         "aien_paged_attention_decode": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_masked": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, I, P, P],
-        "aien_paged_attention_decode_terms": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P, P, P, L, P],
-        "aien_paged_attention_prefill_tc_terms": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P, P, P, L, P],
+        "aien_paged_attention_decode_terms": [P, L, P, P, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P, P, P, L, F, P],
+        "aien_paged_attention_prefill_tc_terms": [P, L, I, P, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, I, F, P, L, I, I, I, P, P, P, P, L, F, P],
         "aien_paged_attention_decode_stream": [P, L, P, P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, F, I, I, P],
         "aien_paged_attention_decode_stream_supports": [I, I, I, I, I],
         "aien_attention_decode_stream_error": [],
@@ -928,14 +928,15 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
                            part_out, part_ml, num_q_heads, num_kv_heads, head_dim, page_size, window, scale,
                            max_splits, token_list=None, num_tokens=None, impl: Optional[str] = None, chunk: int = 0,
                            sinks: Optional[torch.Tensor] = None, head_scale: Optional[torch.Tensor] = None,
-                           slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                           slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Split-key decode attention; the CTA that finishes last merges the chunks.  The ticket
     counters are one small device buffer that every launch finds zero and leaves zero.
     ``impl``: "stream" (TMA ring, persistent CTAs; where the sizes allow) or "direct" (one CTA per
     chunk); both give the same bits.  Default from ``AIEN_B200_DECODE_ATTENTION``, else "stream".
     ``chunk`` > 0 (a token sees only the keys of its own chunk of that many positions; ``max_splits`` then counts
     the 128-key blocks a chunk can touch, see decode_splits) and ``sinks`` (float32 [heads]) are the direct kernel's,
-    and so are the terms per head ``head_scale``, ``slopes`` and ``gate`` (see :func:`paged_attention_generic`)."""
+    and so are the terms per head ``head_scale``, ``slopes`` and ``gate`` and the cap ``softcap`` on the scaled score (see
+    :func:`paged_attention_generic`)."""
     global _ticket_counters
     _dev(q, k_cache, v_cache, block_table, seq_of_token, positions, out, part_out, part_ml, sinks, head_scale, slopes, gate)
     # seq_of_token None: token t belongs to row t of the block table.  token_list: serve only these tokens.
@@ -948,14 +949,14 @@ def paged_attention_decode(q, k_cache, v_cache, block_table, max_blocks, seq_of_
     assert part_out.dtype == torch.float32 and part_out.numel() >= T * num_q_heads * max_splits * head_dim
     assert part_ml.dtype == torch.float32 and part_ml.numel() >= T * num_q_heads * max_splits * 2
     impl = impl or _DECODE_ATTN_IMPL
-    if head_scale is not None or slopes is not None or gate is not None:
+    if head_scale is not None or slopes is not None or gate is not None or softcap:
         assert not chunk and sinks is None
         _check_head_terms(num_q_heads, head_scale, slopes, gate)
         _check(lib().aien_paged_attention_decode_terms(
             _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(block_table), max_blocks, _p(seq_of_token), _p(positions),
             _p(token_list), _p(out), out.stride(0), _p(part_out), _p(part_ml), _p(_ticket_counters), num_q_heads, num_kv_heads, head_dim,
             page_size, window, float(scale), max_splits, T, _p(head_scale), _p(slopes), _p(gate),
-            gate.stride(0) if gate is not None else 0, _stream()), "paged_attention_decode_terms")
+            gate.stride(0) if gate is not None else 0, float(softcap or 0.0), _stream()), "paged_attention_decode_terms")
         return
     if chunk or sinks is not None:
         assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
@@ -1166,7 +1167,7 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
                             out, num_q_heads, num_kv_heads, head_dim, page_size, window, scale, impl: Optional[str] = None,
                             scratch: Optional[torch.Tensor] = None, max_ctx: int = 0, splits: int = 0, chunk: int = 0,
                             sinks: Optional[torch.Tensor] = None, head_scale: Optional[torch.Tensor] = None,
-                            slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                            slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Causal attention of portions of prompts over their requests' pages (bfloat16, tensor
     cores).  ``tile_seq``/``tile_q0``: for every 128-token query tile, the index of its request in
     the step and the tile's offset inside that request's portion.  ``impl``: "tc" (tcgen05, where
@@ -1177,9 +1178,10 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
     its own chunk of that many positions) and ``sinks`` (float32 [heads], one more term exp(sink) in
     the softmax denominator): both kernels take them; the tcgen05 kernel then keeps every tile's keys in one range.
     ``head_scale``, ``slopes``, ``gate`` (see :func:`paged_attention_generic`): the tcgen05 kernel's alone; it keeps
-    every tile's keys in one range with these too."""
+    every tile's keys in one range with these too.  ``softcap`` c > 0 (the scaled score s becomes c * tanh(s / c)): the
+    tcgen05 kernel's alone; it leaves the key ranges as they are."""
     _dev(q, k_cache, v_cache, block_table, q_start, ctx_len, tile_seq, tile_q0, out, sinks, head_scale, slopes, gate)
-    terms = head_scale is not None or slopes is not None or gate is not None
+    terms = head_scale is not None or slopes is not None or gate is not None or bool(softcap)
     _check_head_terms(num_q_heads, head_scale, slopes, gate)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == num_q_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
@@ -1196,7 +1198,7 @@ def paged_attention_prefill(q, k_cache, v_cache, block_table, max_blocks, q_star
             _p(ctx_len), _p(tile_seq), _p(tile_q0), num_tiles, _p(out), out.stride(0), num_q_heads, num_kv_heads, head_dim,
             page_size, window, float(scale), _p(scratch) if scratch is not None else None,
             scratch.numel() * 4 if scratch is not None else 0, int(max_ctx), int(splits), int(chunk), _p(sinks),
-            _p(head_scale), _p(slopes), _p(gate), gate.stride(0) if gate is not None else 0, _stream()),
+            _p(head_scale), _p(slopes), _p(gate), gate.stride(0) if gate is not None else 0, float(softcap or 0.0), _stream()),
             "paged_attention_prefill_tc")
         return
     if terms:
@@ -1867,18 +1869,58 @@ def scale_rows(o: torch.Tensor, mult: float, out: torch.Tensor) -> None:
 
 # ---------------------------------------------------------------------------- attention with a capped score
 def capped_attention_workspace_bytes(lim, num_heads: int, value_dim: int) -> int:
-    """Scratch of :func:`capped_attention` for the largest step."""
-    return biased_attention_workspace_bytes(lim, num_heads, value_dim, 0)
+    """Scratch of :func:`capped_attention` for the largest step: the partial results of the split-key kernel and of the
+    key ranges of the tcgen05 kernel."""
+    return biased_attention_workspace_bytes(lim, num_heads, value_dim, 0) + attention_workspace_bytes(lim, num_heads, value_dim)
 
 
 def capped_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, group, out: torch.Tensor, num_q_heads: int,
                      num_kv_heads: int, head_dim: int, value_dim: int, window: int, scale: float, softcap: float) -> None:
     """Causal attention of the step's tokens over one cache group with the scaled score s turned into softcap * tanh(s /
-    softcap) (softcap 0: left as it is), an optional window, values of size ``value_dim``."""
+    softcap) (softcap 0: left as it is), an optional window, values of size ``value_dim``.  Picks the kernel for the step:
+    in bfloat16 with values as large as keys, portions of prompts go through the tcgen05 kernel and tokens that come alone
+    through the split-key kernel; all else through the plain one."""
     k2 = k_cache.view(-1, num_kv_heads, head_dim)
     v2 = v_cache.view(-1, num_kv_heads, value_dim)
-    paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out,
-                            num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim, softcap=softcap)
+    fast = (_FORCE_ATTN != "generic" and value_dim == head_dim and out.dtype == torch.bfloat16
+            and decode_attention_supports(q, k2, num_q_heads, num_kv_heads, head_dim))
+    splits = max(1, (ctx.max_ctx_len + DECODE_CHUNK - 1) // DECODE_CHUNK)
+
+    def single_tokens(tokens, n):
+        part_out = ctx.workspace.take((n * num_q_heads * splits * head_dim,), torch.float32)
+        part_ml = ctx.workspace.take((n * num_q_heads * splits * 2,), torch.float32)
+        paged_attention_decode(q, k2, v2, group.block_table, group.max_blocks, None if tokens is None else ctx.seq_of_token,
+                               ctx.positions, out, part_out, part_ml, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale,
+                               splits, token_list=tokens, num_tokens=n, impl="direct", softcap=softcap)
+
+    def plain(tokens=None, n=None):
+        paged_attention_generic(q, k2, v2, group.block_table, group.max_blocks, ctx.seq_of_token, ctx.positions, out, num_q_heads,
+                                num_kv_heads, head_dim, group.page_size, window, scale, value_dim=value_dim, softcap=softcap,
+                                token_list=tokens, num_tokens=n)
+
+    splits_ok = fast and decode_masked_takes(num_q_heads, num_kv_heads, head_dim, splits)
+    if ctx.decode_only and splits_ok:
+        single_tokens(None, q.shape[0])
+        return
+    if (not ctx.decode_only and fast and ctx.prefill_tiles is not None and _PREFILL_IMPL == "tc"
+            and prefill_tc_supports(q, out, head_dim, group.page_size)):
+        tile_seq, tile_q0, n = ctx.prefill_tiles
+        if n > 0:
+            scratch = None
+            if n <= PREFILL_SPLIT_MAX_TILES:
+                nbytes = prefill_split_scratch_bytes(n, num_q_heads, head_dim, ctx.max_ctx_len)
+                scratch = ctx.workspace.take((nbytes // 4,), torch.float32) if nbytes else None
+            paged_attention_prefill(q, k2, v2, group.block_table, group.max_blocks, ctx.q_start, ctx.ctx_len, tile_seq, tile_q0, n,
+                                    out, num_q_heads, num_kv_heads, head_dim, group.page_size, window, scale, impl="tc",
+                                    scratch=scratch, max_ctx=ctx.max_ctx_len, softcap=softcap)
+        tokens, nd = ctx.single_tokens if ctx.single_tokens is not None else (None, 0)
+        if nd > 0 and splits_ok:
+            single_tokens(tokens, nd)
+        elif nd > 0:
+            plain(tokens, nd)
+        return
+    plain()
+
 
 
 def routed_combine(parts: torch.Tensor, h: Optional[torch.Tensor], w_same: Optional[torch.Tensor], shared: Optional[torch.Tensor],
