@@ -17,14 +17,14 @@
 namespace aien {
 
 template <typename TD, typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 scaled_add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int nparts, size_t part_stride,
                           const float* __restrict__ vec, const float* __restrict__ bias, const void* __restrict__ w, int wdt,
                           float eps, TO* __restrict__ out, int H) {
     __shared__ float red[32];
     const size_t row = (size_t)blockIdx.x * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += 256) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[row + i];
         if (delta != nullptr) {
             float d = 0.f;
@@ -37,7 +37,7 @@ scaled_add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, i
     }
     if (out == nullptr) return;
     const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += 256) out[row + i] = from_f<TO>(x[row + i] * r * load_dyn(w, wdt, i));
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[row + i] = from_f<TO>(x[row + i] * r * load_dyn(w, wdt, i));
 }
 
 __global__ void __launch_bounds__(256)
@@ -104,8 +104,10 @@ AIEN_API int aien_scaled_add_rmsnorm(float* x, const void* delta, int d_dt, int 
                                      cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || (delta != nullptr && nparts <= 0)) return AIEN_E_SHAPE;
+    // a step of few tokens has too few CTAs to hide a row's loads behind one another: wide CTAs then
+    const int threads = (T <= 2 * 148 && H >= 1024) ? 1024 : 256;
     AIEN_DISPATCH_DTYPE(d_dt, TD, AIEN_DISPATCH_DTYPE(o_dt, TO,
-        (scaled_add_rmsnorm_kernel<TD, TO><<<T, 256, 0, stream>>>(x, (const TD*)delta, nparts, part_stride, vec, bias, w, w_dt, eps, (TO*)out, H))));
+        (scaled_add_rmsnorm_kernel<TD, TO><<<T, threads, 0, stream>>>(x, (const TD*)delta, nparts, part_stride, vec, bias, w, w_dt, eps, (TO*)out, H))));
     return launch_status();
 }
 

@@ -188,7 +188,7 @@ def _declare(l: ctypes.CDLL) -> None:
                                               I, I, I, I, I, F, I, I, P],
         "aien_conv_act": [P, L, I, I, P, I, P, I, I, I, P, c_size_t, P, P, P, P, P, L, I, P],
         "aien_selective_scan": [P, L, P, L, P, L, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, I, L, I, I, I, I, I, I, P, P],
-        "aien_ssd_scan": [P, L, I, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, L, I, I, I, I, I, I, I, I, P, P],
+        "aien_ssd_scan": [P, L, I, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, L, I, I, I, I, I, I, I, I, P, P, P],
         "aien_gate_group_norm": [P, L, P, L, P, I, F, F, P, I, L, I, I, I, P],
         "aien_scaled_add_rmsnorm": [P, P, I, I, c_size_t, P, P, P, I, F, P, I, I, I, P],
         "aien_pass_input": [P, P, P, I, I, I, P],
@@ -1727,10 +1727,15 @@ def conv_act(proj: torch.Tensor, off: int, channels: int, w: torch.Tensor, bias:
 SCAN_SEGMENT_MIN_TOKENS = 128        # steps with fewer tokens walk every portion in one piece
 
 
-def scan_segments(num_tokens: int, decode_only: bool) -> tuple:
+SCAN_FULL_THREADS = 32768            # lanes that fill the GPU without cutting portions
+
+
+def scan_segments(num_tokens: int, decode_only: bool, parallel: int = 0) -> tuple:
     """(segment length, most segments a portion has) for the portion-parallel recurrences of a step; (0, 1): one piece.
-    It depends on the step's token count alone, so that steps of equal shape launch alike."""
-    if decode_only or num_tokens < SCAN_SEGMENT_MIN_TOKENS:
+    ``parallel``: the lanes the recurrence has without cutting (requests x state columns x lanes a column); with enough of
+    them a portion stays whole.  It depends on the step's token and request counts alone, so that steps of equal shape
+    launch alike."""
+    if decode_only or num_tokens < SCAN_SEGMENT_MIN_TOKENS or parallel >= SCAN_FULL_THREADS:
         return 0, 1
     seg = 64
     while seg * 32 < num_tokens:
@@ -1758,7 +1763,8 @@ def selective_scan(x: torch.Tensor, dtz: torch.Tensor, bc: torch.Tensor, b_off: 
                    scratch: Optional[torch.Tensor] = None) -> None:
     """The selective scan over every request's portion: per channel c and state n, token by token,
     dt = softplus(dtz[c] + dt_bias[c]); S[c, n] = exp(dt * A[c, n]) * S[c, n] + dt * x[c] * B[n]; y[c] = sum_n S[c, n] * C[n]
-    + D[c] * x[c]; out[c] = y[c] * silu(z[c]).  x, dtz, z float32 [T, inner] (row strides free); B and C are the N numbers
+    + D[c] * x[c]; out[c] = y[c] * silu(z[c]).  x, dtz, z float32 [T, inner] (row strides free; dtz is overwritten with the
+    step sizes); B and C are the N numbers
     from columns ``b_off`` / ``c_off`` of the float32 rows ``bc``; A float32 [inner, N]; S lives in the request's state row
     from ``s_off`` on ([inner, N]) and starts from zeros where a portion's first token has position 0."""
     _dev(x, dtz, bc, z, A, dt_bias, D, state, slot_map, q_start, positions, out, scratch)
@@ -1773,19 +1779,23 @@ def selective_scan(x: torch.Tensor, dtz: torch.Tensor, bc: torch.Tensor, b_off: 
                                      _p(A), _p(dt_bias), _p(D), dt(D), _p(state), state.stride(0), int(s_off), _p(slot_map), _p(q_start),
                                      _p(positions), _p(out), dt(out), out.stride(0), T, int(num_seqs), inner, int(N), int(seg_len), int(nseg),
                                      _p(scratch), _stream()), "selective_scan")
-    if seg_len and nseg > 1:
-        add_launches(2)
+    add_launches(3 if (seg_len and nseg > 1) else 1)
 
 
 def ssd_scan(xbc: torch.Tensor, x_off: int, b_off: int, c_off: int, dtr: torch.Tensor, A: torch.Tensor, dt_bias: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, s_off: int, slot_map: torch.Tensor, q_start: torch.Tensor, positions: torch.Tensor, y: torch.Tensor,
-             num_seqs: int, heads: int, V: int, G: int, N: int, seg_len: int = 0, nseg: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
+             num_seqs: int, heads: int, V: int, G: int, N: int, seg_len: int = 0, nseg: int = 1, scratch: Optional[torch.Tensor] = None,
+             steps: Optional[torch.Tensor] = None) -> None:
     """The state-space-duality recurrence over every request's portion: per head h (group g = h // (heads // G)), token by
     token, dt = softplus(dtr[h] + dt_bias[h]); S = exp(-A[h] * dt) * S + dt * B[g] x[h]^T (S is N x V); y[h] = S^T C[g] +
     D[h] * x[h].  x, B, C are column blocks of the float32 rows ``xbc``; dtr float32 [T, heads] (row stride free); A float32
-    [heads]; S lives in the request's state row from ``s_off`` on ([heads, N, V]); y float32 [T, heads * V]."""
-    _dev(xbc, dtr, A, dt_bias, D, state, slot_map, q_start, positions, y, scratch)
+    [heads]; S lives in the request's state row from ``s_off`` on (as [heads, V, N]); y float32 [T, heads * V].  ``steps``:
+    float32 scratch of T * 2 * heads numbers (made here when not given)."""
+    _dev(xbc, dtr, A, dt_bias, D, state, slot_map, q_start, positions, y, scratch, steps)
     T = xbc.shape[0]
+    if steps is None:
+        steps = torch.empty(T * 2 * heads, dtype=torch.float32, device=xbc.device)
+    assert steps.dtype == torch.float32 and steps.is_contiguous() and steps.numel() >= T * 2 * heads
     assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and dtr.dtype == torch.float32 and dtr.stride(1) == 1
     assert A.dtype == torch.float32 and A.numel() == heads and dt_bias.dtype == D.dtype and dt_bias.is_contiguous() and D.is_contiguous()
     assert state.dtype == torch.float32 and state.stride(-1) == 1 and y.dtype == torch.float32 and y.stride(1) == 1
@@ -1793,9 +1803,8 @@ def ssd_scan(xbc: torch.Tensor, x_off: int, b_off: int, c_off: int, dtr: torch.T
         assert scratch is not None and scratch.numel() >= 2 * (T // seg_len + num_seqs) * heads * N * V
     _check(lib().aien_ssd_scan(_p(xbc), xbc.stride(0), int(x_off), int(b_off), int(c_off), _p(dtr), dtr.stride(0), _p(A), _p(dt_bias), _p(D),
                                dt(D), _p(state), state.stride(0), int(s_off), _p(slot_map), _p(q_start), _p(positions), _p(y), y.stride(0),
-                               T, int(num_seqs), int(heads), int(V), int(G), int(N), int(seg_len), int(nseg), _p(scratch), _stream()), "ssd_scan")
-    if seg_len and nseg > 1:
-        add_launches(2)
+                               T, int(num_seqs), int(heads), int(V), int(G), int(N), int(seg_len), int(nseg), _p(scratch), _p(steps), _stream()), "ssd_scan")
+    add_launches(3 if (seg_len and nseg > 1) else 1)
 
 
 def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, mult: float, out: torch.Tensor, groups: int) -> None:

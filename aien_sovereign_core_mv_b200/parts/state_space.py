@@ -55,9 +55,10 @@ class BranchMixer(Mixer):
         return linear(ctx, y, self.out_weight(), out_dtype=torch.float32, may_defer_sum=True)
 
 
-def _segments(ctx: StepContext, lanes: int):
-    """(segment length, segments, scratch) of the portion-parallel recurrences for this step."""
-    seg, nseg = K.scan_segments(ctx.num_tokens, ctx.decode_only)
+def _segments(ctx: StepContext, lanes: int, parallel: int):
+    """(segment length, segments, scratch) of the portion-parallel recurrences for this step; ``lanes``: state values a
+    request, ``parallel``: lanes a request gives the kernel without cutting."""
+    seg, nseg = K.scan_segments(ctx.num_tokens, ctx.decode_only, parallel * ctx.num_seqs)
     if not seg:
         return 0, 1, None
     return seg, nseg, ctx.workspace.take((2 * (ctx.num_tokens // seg + ctx.num_seqs) * lanes,), torch.float32)
@@ -123,7 +124,7 @@ class SelectiveScan(Mixer):
         xp = linear(ctx, xa, self.w_x, out_dtype=torch.float32)                         # dt | B | C
         dtz = linear(ctx, xp[:, :R], self.w_dt, out_dtype=torch.float32)                # float32 step sizes into the softplus
         y = ws.take((T, I), ctx.dtype)
-        seg, nseg, scratch = _segments(ctx, I * N)
+        seg, nseg, scratch = _segments(ctx, I * N, I * min(N, 16))
         K.selective_scan(x, dtz, xp, R, R + N, proj[:, I:], self.A, self.dt_b, self.D, state, self.conv_floats, group.slot_map,
                          ctx.q_start, ctx.positions, y, ctx.num_seqs, N, seg, nseg, scratch)
         return linear(ctx, y, self.w_o, out_dtype=torch.float32, may_defer_sum=True)
@@ -139,7 +140,7 @@ class StateSpaceDuality(BranchMixer):
     silu(z), cut into ``norm_groups`` equal parts that are each divided by their own root mean square (``norm_eps`` inside
     the root), multiplied by the weight ``norm`` and projected by W_o.
 
-    One float32 state slot per request holds the convolution's last taps - 1 inputs followed by S [heads, N, value_dim];
+    One float32 state slot per request holds the convolution's last taps - 1 inputs followed by S as [heads, value_dim, N];
     it starts from zeros.  Step sizes, decays, the recurrence, the gate and the norm are float32 in both precisions."""
 
     def __init__(self, hidden_size: int, num_heads: int, value_dim: int, state: int, groups: int = 1, norm_groups: int = 1,
@@ -191,7 +192,7 @@ class StateSpaceDuality(BranchMixer):
         return group.storage["state"][run.slot], group.slot_map
 
     def core_workspace_bytes(self, lim):
-        return lim.max_tokens * (self.channels + self.inner) * 4 + 1024 \
+        return lim.max_tokens * (self.channels + self.inner + 2 * self.num_heads) * 4 + 2048 \
             + 4 * K.scan_scratch_floats(lim.max_tokens, lim.max_seqs, self.num_heads * self.state * self.value_dim)
 
     def core(self, ctx, proj, col0, store, out, out_col0, mult):
@@ -202,10 +203,11 @@ class StateSpaceDuality(BranchMixer):
         K.conv_act(proj, col0 + I, self.channels, self.conv, self.conv_b, self.taps, "silu", state, slots, ctx.seq_of_token, ctx.q_start,
                    ctx.positions, xbc)
         y = ws.take((T, I), torch.float32)
-        seg, nseg, scratch = _segments(ctx, self.num_heads * self.state * self.value_dim)
+        seg, nseg, scratch = _segments(ctx, self.num_heads * self.state * self.value_dim, I * min(self.state, 32))
+        steps = ws.take((T * 2 * self.num_heads,), torch.float32)
         dt0 = col0 + 2 * I + 2 * GN
         K.ssd_scan(xbc, 0, I, I + GN, proj[:, dt0:dt0 + self.num_heads], self.A, self.dt_b, self.D, state, self.conv_floats, slots,
-                   ctx.q_start, ctx.positions, y, ctx.num_seqs, self.num_heads, self.value_dim, self.groups, self.state, seg, nseg, scratch)
+                   ctx.q_start, ctx.positions, y, ctx.num_seqs, self.num_heads, self.value_dim, self.groups, self.state, seg, nseg, scratch, steps)
         K.gate_group_norm(y, proj[:, col0:col0 + I], self.norm_w, self.norm_eps, mult, out[:, out_col0:out_col0 + I], self.norm_groups)
 
 

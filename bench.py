@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Headline measurement: decode tokens per second of the Qwen3-8B-shaped model on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun|ripesun|botalorn]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--prompt-len L] [--prefill-tokens T] [--layers N] [--workload decode|llama3_8b|serving|mixed_step|dulisun|ripesun|botalorn|mumazen]
 
 A step is one decode step of a batch of requests that each hold a 1,024-token prompt (context
 limit 4,096, pages of 16 tokens), random bfloat16 weights, synthetic uniform token ids.  One JSON
@@ -570,6 +570,112 @@ def botalorn_workload(only: str = "") -> int:
     return 0
 
 
+def _mumazen_config(width, heads, kv, dim, inner, scan_state, ssd_heads, ssd_vdim, ssd_state, ff, experts, identity, top, expert_ff, layers, vocab):
+    scan = {"type": "mamba1", "mixer": {"inner": inner, "state": scan_state, "dt_rank": max(1, width // 16), "conv": 4},
+            "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+                 "rot": {"base": 1000000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}},
+        "right": {"heads": ssd_heads, "vdim": ssd_vdim, "state": ssd_state, "groups": 1, "norm_groups": 1, "conv": 4},
+        "left_scale": 1.0, "right_scale": 1.0},
+        "mlp": {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top},
+                "shared": {"ff": expert_ff}}}
+    return {"architecture": "Mumazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "residual_mult": 1.0, "layers": [scan if i % 2 == 0 else par for i in range(layers)]}
+
+
+# (name, Mumazen sizes); layers alternate the selective scan (dense feed-forward) and attention beside the state-space-duality
+# recurrence (routed feed-forward: `top` of `experts` + `identity` outputs, a shared expert).  Beside each: the Botalorn
+# model of the same width, heads, head size, feed-forward size, layers and vocabulary (delta rule and windowed attention over
+# convolved projections, four streams), and the dense Qwen3-style model of equal per-token feed-forward arithmetic.
+MUMAZEN_SHAPES = (
+    ("w2048_h16", dict(width=2048, heads=16, kv=4, dim=128, inner=4096, scan_state=16, ssd_heads=32, ssd_vdim=64, ssd_state=128, ff=4096,
+                       experts=16, identity=2, top=4, expert_ff=1024, layers=6, vocab=32768)),
+    ("w4096_h32", dict(width=4096, heads=32, kv=8, dim=128, inner=8192, scan_state=16, ssd_heads=64, ssd_vdim=64, ssd_state=128, ff=8192,
+                       experts=16, identity=2, top=4, expert_ff=2048, layers=4, vocab=32768)),
+    ("w1024_h16", dict(width=1024, heads=16, kv=4, dim=64, inner=2048, scan_state=16, ssd_heads=16, ssd_vdim=64, ssd_state=64, ff=2048,
+                       experts=8, identity=1, top=2, expert_ff=1024, layers=6, vocab=32768)),
+)
+
+
+def mumazen_workload(only: str = "") -> int:
+    """Prefill and decode throughput of the Mumazen design at a few sizes that resemble a real model's layers (random
+    bfloat16 weights), each beside the Botalorn model and the dense Qwen3-style model of equal size.  Prefill: one prompt
+    of 2,048 tokens; decode: 8 and 64 requests at 1,024 tokens of context, captured graphs.  Timed on the device with CUDA
+    events after warm-up; every step reads more weights than L2 holds.  The timed steps lie between cudaProfilerStart and
+    cudaProfilerStop."""
+    import torch
+    from aien_sovereign_core_mv_b200 import Engine, EngineConfig
+    from aien_sovereign_core_mv_b200 import kernels as K
+    results = []
+    P, CTX = 2048, 1024
+    which_only = os.environ.get("AIEN_BENCH_MODELS", "").split(",") if os.environ.get("AIEN_BENCH_MODELS") else None
+    for name, sz in MUMAZEN_SHAPES:
+        if only and only != name:
+            continue
+        bff = int(round(1.5 * sz["ff"] / 256)) * 256                 # two matrices of bff against three of ff
+        inter = sz["ff"]
+        dense = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=sz["layers"], hidden_size=sz["width"],
+                     num_attention_heads=sz["heads"], num_key_value_heads=sz["kv"], head_dim=sz["dim"], intermediate_size=inter,
+                     vocab_size=sz["vocab"], rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                     max_position_embeddings=8192, hidden_act="silu", attention_bias=False, eos_token_id=0)
+        botalorn = _botalorn_config(width=sz["width"], heads=sz["heads"], kv=sz["kv"], dim=sz["dim"], vdim=sz["dim"], window=CTX, taps=4,
+                                    streams=4, ff=bff, layers=sz["layers"], vocab=sz["vocab"])
+        row = {"shape": name, "sizes": dict(sz), "botalorn_ff": bff, "dense_intermediate": inter}
+        for which, cfg in (("mumazen", _mumazen_config(**sz)), ("botalorn", botalorn), ("dense", dense)):
+            if which_only and which not in which_only:
+                continue
+            ec = EngineConfig(dtype="bfloat16", page_size=16, max_cache_tokens=64 * (CTX + 64) + P + 64, max_requests=64,
+                              max_batch_tokens=P, max_context=4096, max_batch_size=64)
+            eng = Engine.from_config(cfg, seed=5, engine_config=ec, init_std=0.02, device_init=True)
+            V = sz["vocab"]
+            toks = lambda n, s: [(7 * i + 13 * s) % V for i in range(n)]
+
+            def timed(fn, warm, reps):
+                for i in range(warm):
+                    fn(i)
+                torch.cuda.synchronize()
+                ms = []
+                for i in range(reps):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    fn(warm + i)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms.append(e0.elapsed_time(e1))
+                return sorted(ms)[len(ms) // 2]
+
+            def prefill(i):
+                eng.step([(9000 + i, toks(P, i), [P - 1])])
+                eng.end_request(9000 + i)
+
+            out = {}
+            torch.cuda.profiler.start()
+            t = timed(prefill, 3, 5)
+            out["prefill_2048"] = {"ms": round(t, 3), "tokens_per_s": round(P / t * 1e3, 1)}
+            for batch in (8, 64):
+                for r in range(0, batch, 2):
+                    eng.step([(r, toks(CTX, r), []), (r + 1, toks(CTX, r + 1), [])])
+                t = timed(lambda i: eng.step([(r, [(i + r) % V], [0]) for r in range(batch)]), 4, 12)
+                out[f"decode_b{batch}"] = {"ms": round(t, 3), "tokens_per_s": round(batch / t * 1e3, 1)}
+                for r in range(batch):
+                    eng.end_request(r)
+            torch.cuda.profiler.stop()
+            eng.check_waits()
+            out["wait_errors"] = sum(1 for w in K.read_wait_errors() if w != 0)
+            out["weight_bytes"] = int(sum(t.numel() * t.element_size() for p in eng.model.parts() for t in vars(p).values()
+                                          if isinstance(t, torch.Tensor) and t.dim() >= 2))
+            row[which] = out
+            del eng
+            torch.cuda.empty_cache()
+        results.append(row)
+    print(json.dumps({"metric": "mumazen_beside_botalorn_and_dense", "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True,
+                      "dtype": "bf16", "data": "synthetic", "impl": "ours", "shapes": results,
+                      "config": {"prefill_tokens": P, "decode_context": CTX, "page_size": 16, "seed": 5,
+                                 "l2": "weights read per step exceed L2"}}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -588,17 +694,18 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=0, help="top-k of the end-to-end run")
     ap.add_argument("--align-step-tokens", type=int, default=0,
                     help="serving workload: the scheduler cuts portions so that a step's tokens fill whole tiles of this many rows")
-    ap.add_argument("--shape", default="", help="dulisun, ripesun and botalorn workloads: only this shape (default: all)")
+    ap.add_argument("--shape", default="", help="dulisun, ripesun, botalorn and mumazen workloads: only this shape (default: all)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun", "ripesun", "botalorn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "llama3_8b", "serving", "mixed_step", "dulisun", "ripesun", "botalorn", "mumazen"],
                     help="decode: the headline decode-step measurement (Qwen3-8B shape, 1,024-token prompts); llama3_8b: the same "
                          "line for the Llama-3-8B shape, 16 requests at contexts ending at 8,192 tokens; serving: continuous batching "
                          "of 32 requests on the Qwen3-4B shape (prompts of 64..4096 tokens, portions of 512, 256 new tokens each); "
                          "mixed_step: one step of a 512-token portion beside 24 decoding requests on that shape, timed alone; "
                          "dulisun: prefill and decode of the Dulisun design at a few sizes beside the dense model of equal size; "
-                         "ripesun: the same for the Ripesun design; botalorn: the Botalorn design beside Ripesun and the dense model")
+                         "ripesun: the same for the Ripesun design; botalorn: the Botalorn design beside Ripesun and the dense model; "
+                         "mumazen: the Mumazen design beside Botalorn and the dense model")
     ap.add_argument("--fill", default="prefill", choices=["prefill", "cache"],
                     help="how requests get their prompt: real prefill, or (development only) cache pages "
                          "filled with random keys/values without running the model")
@@ -622,6 +729,8 @@ def main() -> int:
         return ripesun_workload(args.shape)
     if args.workload == "botalorn":
         return botalorn_workload(args.shape)
+    if args.workload == "mumazen":
+        return mumazen_workload(args.shape)
 
     import numpy as np
     import torch
