@@ -49,6 +49,33 @@ step_sizes_kernel(float* __restrict__ dtz, long lddt, const void* __restrict__ b
 
 // LANES neighbouring lanes share one channel: lane ln keeps the CH state values n = ln * CH .. ln * CH + CH - 1 in
 // registers (N <= LANES * CH) and the partial sums of y meet by shuffles.  U tokens are fetched ahead of their arithmetic.
+// The rows U tokens bring to one lane of the selective scan.
+template <int U, int CH>
+struct ScanRows {
+    float dt[U], x[U], z[U], b[U][CH], c[U][CH];
+    __device__ __forceinline__ void fetch(const float* __restrict__ xs, long ldx, const float* __restrict__ dtv, long lddt,
+                                          const float* __restrict__ zs, long ldz, const float* __restrict__ bc, long ldbc, int b_off,
+                                          int c_off, int ch, int n0, int N, int t, int t1, bool wants_z) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int tt = t + u < t1 ? t + u : t1 - 1;            // beyond the portion's end the last token's rows are read again
+            dt[u] = dtv[(size_t)tt * lddt + ch];
+            x[u] = xs[(size_t)tt * ldx + ch];
+            z[u] = wants_z ? zs[(size_t)tt * ldz + ch] : 0.f;
+            const float* br = bc + (size_t)tt * ldbc + b_off + n0;
+            const float* cr = bc + (size_t)tt * ldbc + c_off + n0;
+#pragma unroll
+            for (int i = 0; i < CH; ++i) { const bool in = n0 + i < N; b[u][i] = in ? br[i] : 0.f; c[u][i] = in ? cr[i] : 0.f; }
+        }
+    }
+};
+
+// exp for the decays: full precision where the result leaves in float32; through the special-function unit (relative
+// error near 2^-21) where it leaves in bfloat16, whose own rounding is a hundred times coarser.
+template <typename TO> __device__ __forceinline__ float decay_exp(float v);
+template <> __device__ __forceinline__ float decay_exp<float>(float v) { return expf(v); }
+template <> __device__ __forceinline__ float decay_exp<__nv_bfloat16>(float v) { return __expf(v); }
+
 template <int LANES, int CH, int U, typename TO>
 __global__ void __launch_bounds__(SSM_THREADS)
 selective_scan_kernel(const float* __restrict__ x, long ldx, const float* __restrict__ dtv, long lddt,
@@ -84,38 +111,33 @@ selective_scan_kernel(const float* __restrict__ x, long ldx, const float* __rest
         S[i] = (in && !zero) ? init[i] : 0.f;
     }
     const float dskip = load_dyn(D, pdt, c);
+    const bool wants_z = ln == 0 && sg.mode != 1;
+    // The rows of U tokens are fetched while the U tokens before them are worked on (two sets of registers): at the few
+    // warps a scheduler has here, a fetch that started only after the arithmetic would be waited for in full.
+    ScanRows<U, CH> cur, nxt;
+    if (t0 < t1) cur.fetch(x, ldx, dtv, lddt, z, ldz, bc, ldbc, b_off, c_off, c, n0, N, t0, t1, wants_z);
     for (int t = t0; t < t1; t += U) {
-        float dtu[U], xu[U], zu[U], bu[U][CH], cu[U][CH];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int tt = t + u < t1 ? t + u : t1 - 1;
-            dtu[u] = dtv[(size_t)tt * lddt + c];
-            xu[u] = x[(size_t)tt * ldx + c];
-            zu[u] = (ln == 0 && sg.mode != 1) ? z[(size_t)tt * ldz + c] : 0.f;
-            const float* br = bc + (size_t)tt * ldbc + b_off + n0;
-            const float* cr = bc + (size_t)tt * ldbc + c_off + n0;
-#pragma unroll
-            for (int i = 0; i < CH; ++i) { const bool in = n0 + i < N; bu[u][i] = in ? br[i] : 0.f; cu[u][i] = in ? cr[i] : 0.f; }
-        }
+        if (t + U < t1) nxt.fetch(x, ldx, dtv, lddt, z, ldz, bc, ldbc, b_off, c_off, c, n0, N, t + U, t1, wants_z);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (t + u < t1) {
-                const float dt = dtu[u], dx = dt * xu[u];
+                const float dt = cur.dt[u], dx = dt * cur.x[u];
                 float y = 0.f;
 #pragma unroll
                 for (int i = 0; i < CH; ++i) {
-                    const float e = expf(dt * a[i]);
-                    S[i] = fmaf(e, S[i], dx * bu[u][i]);
+                    const float e = decay_exp<TO>(dt * a[i]);
+                    S[i] = fmaf(e, S[i], dx * cur.b[u][i]);
                     if (sg.mode == 1) P[i] *= e;
-                    y = fmaf(S[i], cu[u][i], y);
+                    y = fmaf(S[i], cur.c[u][i], y);
                 }
                 if (sg.mode != 1) {
 #pragma unroll
                     for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-                    if (ln == 0 && live) out[(size_t)(t + u) * ldo + c] = from_f<TO>(fmaf(dskip, xu[u], y) * ssm_silu(zu[u]));
+                    if (ln == 0 && live) out[(size_t)(t + u) * ldo + c] = from_f<TO>(fmaf(dskip, cur.x[u], y) * ssm_silu(cur.z[u]));
                 }
             }
         }
+        cur = nxt;
     }
     if (!live || !mine) return;
     if (sg.mode == 1) {
@@ -318,6 +340,17 @@ template <typename TO>
 static int dispatch_selective_scan(const ScanArgs& a) {
     const int N = a.N;
     if (N > 128) return AIEN_E_SHAPE;
+    if (a.T == a.S) {
+        // single tokens: a CTA lives for one token, so what counts is how many are resident and how much each moves:
+        // four lanes a channel, no rows fetched ahead (fewer registers)
+        if (N <= 4) launch_selective_scan<4, 1, 1, TO>(a);
+        else if (N <= 8) launch_selective_scan<4, 2, 1, TO>(a);
+        else if (N <= 16) launch_selective_scan<4, 4, 1, TO>(a);
+        else if (N <= 32) launch_selective_scan<4, 8, 1, TO>(a);
+        else if (N <= 64) launch_selective_scan<16, 4, 1, TO>(a);
+        else launch_selective_scan<16, 8, 1, TO>(a);
+        return 0;
+    }
     if (N <= 2) launch_selective_scan<1, 2, 4, TO>(a);
     else if (N <= 8) launch_selective_scan<4, 2, 4, TO>(a);
     else if (N <= 16) launch_selective_scan<16, 1, 4, TO>(a);
@@ -398,6 +431,15 @@ AIEN_API int aien_ssd_scan(const float* xbc, long ld, int x_off, int b_off, int 
     // float4 moves: every lane's first state value, B and C value on a 16-byte boundary, whole groups of four inside N
     const bool vec = N >= 128 && N % 4 == 0 && ld % 4 == 0 && b_off % 4 == 0 && c_off % 4 == 0 && state_stride % 4 == 0 && s_off % 4 == 0 &&
                      ((uintptr_t)xbc & 15) == 0 && ((uintptr_t)state & 15) == 0 && (scratch == nullptr || ((uintptr_t)scratch & 15) == 0);
+    if (T == S) {                                     // single tokens: no rows fetched ahead (fewer registers, more CTAs resident)
+        if (N <= 8) launch_ssd_scan<8, 1, 1, false>(a);
+        else if (N <= 16) launch_ssd_scan<8, 2, 1, false>(a);
+        else if (N <= 32) launch_ssd_scan<32, 1, 1, false>(a);
+        else if (N <= 64) launch_ssd_scan<32, 2, 1, false>(a);
+        else if (N <= 128) { if (vec) launch_ssd_scan<32, 4, 1, true>(a); else launch_ssd_scan<32, 4, 1, false>(a); }
+        else { if (vec && N % 8 == 0) launch_ssd_scan<32, 8, 1, true>(a); else launch_ssd_scan<32, 8, 1, false>(a); }
+        return launch_status();
+    }
     if (N <= 8) launch_ssd_scan<8, 1, 4, false>(a);
     else if (N <= 16) launch_ssd_scan<8, 2, 4, false>(a);
     else if (N <= 32) launch_ssd_scan<32, 1, 4, false>(a);

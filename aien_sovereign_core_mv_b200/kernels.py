@@ -1725,36 +1725,32 @@ def conv_act(proj: torch.Tensor, off: int, channels: int, w: torch.Tensor, bias:
 
 
 SCAN_SEGMENT_MIN_TOKENS = 128        # steps with fewer tokens walk every portion in one piece
-
-
-SCAN_FULL_THREADS = 32768            # lanes that fill the GPU without cutting portions
+SCAN_TARGET_LANES = 65536            # with this many lanes at work a portion is walked whole; with fewer it is cut until there are about as many
+SCAN_MIN_SEGMENT = 32                # tokens: shorter segments cost more in their second pass than they win
 
 
 def scan_segments(num_tokens: int, decode_only: bool, parallel: int = 0) -> tuple:
     """(segment length, most segments a portion has) for the portion-parallel recurrences of a step; (0, 1): one piece.
-    ``parallel``: the lanes the recurrence has without cutting (requests x state columns x lanes a column); with enough of
-    them a portion stays whole.  It depends on the step's token and request counts alone, so that steps of equal shape
-    launch alike."""
-    if decode_only or num_tokens < SCAN_SEGMENT_MIN_TOKENS or parallel >= SCAN_FULL_THREADS:
+    ``parallel``: the lanes the recurrence has without cutting (requests x state columns x lanes a column).  A walk over a
+    portion costs its length in dependent steps, so a step with few lanes is cut into segments that run side by side (two
+    passes, each a segment long) until about SCAN_TARGET_LANES lanes are at work; measured at 65,536 lanes, four segments
+    were slower than the whole walk (the second pass repeats every instruction).  It depends on the step's token and
+    request counts alone, so that steps of equal shape launch alike."""
+    if decode_only or num_tokens < SCAN_SEGMENT_MIN_TOKENS:
         return 0, 1
-    seg = 64
-    while seg * 32 < num_tokens:
-        seg *= 2
-    return seg, (num_tokens + seg - 1) // seg
+    want = -(-SCAN_TARGET_LANES // max(int(parallel), 1))
+    want = min(want, num_tokens // SCAN_MIN_SEGMENT)
+    if want <= 2:                                   # two passes over halves win nothing
+        return 0, 1
+    seg = -(-num_tokens // want)
+    return seg, -(-num_tokens // seg)
 
 
-def scan_scratch_floats(max_tokens: int, max_seqs: int, lanes: int) -> int:
-    """Upper bound of the float32 scratch the portion-parallel recurrences take for ``lanes`` state values a request."""
-    worst = 0
-    t = SCAN_SEGMENT_MIN_TOKENS
-    while True:
-        tt = min(t, max_tokens)
-        seg, _ = scan_segments(tt, False)
-        if seg:
-            worst = max(worst, 2 * (tt // seg + max_seqs) * lanes)
-        if t >= max_tokens:
-            return worst
-        t *= 2
+def scan_scratch_floats(max_tokens: int, max_seqs: int, lanes: int, parallel: int = 1) -> int:
+    """Upper bound of the float32 scratch the portion-parallel recurrences take for ``lanes`` state values a request
+    whose recurrence has ``parallel`` lanes a request without cutting."""
+    want = min(-(-SCAN_TARGET_LANES // max(int(parallel), 1)), max(max_tokens // SCAN_MIN_SEGMENT, 1))
+    return 2 * (want + 1 + max_seqs) * lanes
 
 
 def selective_scan(x: torch.Tensor, dtz: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor, A: torch.Tensor,

@@ -106,7 +106,7 @@ class SelectiveScan(Mixer):
     def workspace_bytes(self, lim):
         I, N, R = self.inner, self.state, self.dt_rank
         return lim.max_tokens * ((2 * I + I + (R + 2 * N) + I) * 4 + 2 * I * lim.itemsize + self.hidden_size * 4) + 16384 \
-            + 2 * K.PARTIALS_MAX_BYTES + 4 * K.scan_scratch_floats(lim.max_tokens, lim.max_seqs, I * N)
+            + 2 * K.PARTIALS_MAX_BYTES + 4 * K.scan_scratch_floats(lim.max_tokens, lim.max_seqs, I * N, I * min(N, 16))
 
     def forward(self, ctx: StepContext, h: torch.Tensor, run: RunBinding):
         T, I, N, R = ctx.num_tokens, self.inner, self.state, self.dt_rank
@@ -193,7 +193,7 @@ class StateSpaceDuality(BranchMixer):
 
     def core_workspace_bytes(self, lim):
         return lim.max_tokens * (self.channels + self.inner + 2 * self.num_heads) * 4 + 2048 \
-            + 4 * K.scan_scratch_floats(lim.max_tokens, lim.max_seqs, self.num_heads * self.state * self.value_dim)
+            + 4 * K.scan_scratch_floats(lim.max_tokens, lim.max_seqs, self.num_heads * self.state * self.value_dim, self.inner * min(self.state, 32))
 
     def core(self, ctx, proj, col0, store, out, out_col0, mult):
         T, I, GN = ctx.num_tokens, self.inner, self.groups * self.state
