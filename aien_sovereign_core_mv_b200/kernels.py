@@ -1725,7 +1725,9 @@ def conv_act(proj: torch.Tensor, off: int, channels: int, w: torch.Tensor, bias:
 
 
 SCAN_SEGMENT_MIN_TOKENS = 128        # steps with fewer tokens walk every portion in one piece
-SCAN_TARGET_LANES = 65536            # with this many lanes at work a portion is walked whole; with fewer it is cut until there are about as many
+# with this many lanes at work a portion is walked whole; with fewer it is cut until there are about as many
+# (AIEN_B200_SCAN_LANES pins another number for measurements)
+SCAN_TARGET_LANES = int(__import__("os").environ.get("AIEN_B200_SCAN_LANES", "65536"))
 SCAN_MIN_SEGMENT = 32                # tokens: shorter segments cost more in their second pass than they win
 
 
