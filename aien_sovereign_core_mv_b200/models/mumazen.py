@@ -102,7 +102,8 @@ def _parallel(i: int, mixer: Mapping[str, Any], width: int, eps: float):
     where = f"layers[{i}].mixer"
     left, right = _need(mixer, "left", where), _need(mixer, "right", where)
     lw, rw = where + ".left", where + ".right"
-    heads, kv = _need(left, "heads", lw, int), _need(left, "kv_heads", lw, int)
+    heads = _need(left, "heads", lw, int)
+    kv = _need(left, "kv_heads", lw, int) if left.get("kv_heads") is not None else heads        # no groups named: one key/value head a query head
     if heads % kv:
         raise ConfigError(f"config.json: {lw}.heads {heads} must be a multiple of {lw}.kv_heads {kv}")
     dim = _need(left, "dim", lw, int)
@@ -224,7 +225,7 @@ def _loop(raw: Mapping[str, Any], num_layers: int) -> Optional[Tuple[int, int, i
     if loop is None:
         return None
     start, stop = _opt_count(loop, "start", 0, "loop"), _need(loop, "stop", "loop", int)
-    times = _need(loop, "times", "loop", int)
+    times = _need(loop, "times", "loop", int) if loop.get("times") is not None else 1
     if not (0 <= start < stop <= num_layers):
         raise ConfigError(f"config.json: loop.start {start} and loop.stop {stop} must name a stretch of the {num_layers} layers")
     return start, stop, times
