@@ -238,12 +238,13 @@ delta_conv_prepare_kernel(const float* __restrict__ proj, long ld, int q_off, in
 }
 
 // One block of C convolved channels with a bias and an activation of its own:
-// out[t][c] = f(conv(c) + bias[c]), f the identity (act 0) or silu (act 1); float32 out.
+// out[t][c] = f(conv(c) + bias[c]), f the identity (act 0) or silu (act 1); float32 out, and on request the same rows
+// once more in bfloat16 (the operand of a product that follows).
 __global__ void __launch_bounds__(SC_THREADS_WIDE)
 conv_act_kernel(const float* __restrict__ proj, long ld, int off, int C, const void* __restrict__ w, int wdt,
                 const void* __restrict__ bias, int bdt, int taps, int act, float* __restrict__ state, size_t state_stride,
                 const int* __restrict__ state_slots, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                const int* __restrict__ positions, float* __restrict__ out, long ldo) {
+                const int* __restrict__ positions, float* __restrict__ out, long ldo, __nv_bfloat16* __restrict__ out16, long ldo16) {
     ConvRow r;
     const int rows = conv_rows(blockIdx.x, taps, seq_of_token, q_start, positions, state_slots, r);
     if (rows == 0) return;
@@ -254,7 +255,9 @@ conv_act_kernel(const float* __restrict__ proj, long ld, int off, int C, const v
         for (int c = threadIdx.x; c < C; c += blockDim.x) {
             float y = conv_value(proj, ld, off, c, w, wdt, taps, st, C, 0, r);
             if (bias != nullptr) y += load_dyn(bias, bdt, c);
-            out[(size_t)r.t * ldo + c] = act == 1 ? silu_f(y) : y;
+            y = act == 1 ? silu_f(y) : y;
+            out[(size_t)r.t * ldo + c] = y;
+            if (out16 != nullptr) out16[(size_t)r.t * ldo16 + c] = __float2bfloat16_rn(y);
         }
     }
     __syncthreads();
@@ -324,14 +327,16 @@ AIEN_API int aien_delta_conv_prepare(const float* proj, long ld, int q_off, int 
 }
 
 // proj float32 [T, ld] with the C convolved channels from column `off` on; weights [C, taps] in w_dt, bias [C] in b_dt (or
-// null); state float32 rows of state_stride numbers whose first (taps-1)*C are the convolution's; out float32 [T, ldo].
+// null); state float32 rows of state_stride numbers whose first (taps-1)*C are the convolution's; out float32 [T, ldo];
+// out16 (or null) bfloat16 [T, ldo16]: the same rows rounded.
 AIEN_API int aien_conv_act(const float* proj, long ld, int off, int C, const void* w, int w_dt, const void* bias, int b_dt, int taps,
                            int act, float* state, size_t state_stride, const int* state_slots, const int* seq_of_token,
-                           const int* q_start, const int* positions, float* out, long ldo, int T, cudaStream_t stream) {
+                           const int* q_start, const int* positions, float* out, long ldo, void* out16, long ldo16, int T,
+                           cudaStream_t stream) {
     if (T <= 0) return 0;
     if (taps < 1 || taps > SC_MAX_TAPS || C <= 0 || (act != 0 && act != 1)) return AIEN_E_SHAPE;
     if (taps > 1 && state == nullptr) return AIEN_E_SHAPE;
     conv_act_kernel<<<T, conv_threads(T, C), 0, stream>>>(proj, ld, off, C, w, w_dt, bias, b_dt, taps, act, state, state_stride, state_slots,
-                                                          seq_of_token, q_start, positions, out, ldo);
+                                                          seq_of_token, q_start, positions, out, ldo, (__nv_bfloat16*)out16, ldo16);
     return launch_status();
 }

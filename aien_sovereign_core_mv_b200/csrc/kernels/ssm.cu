@@ -2,11 +2,12 @@
 // state-space-duality form (a state matrix per head), and the gate and grouped norm that follows the latter.
 //
 //   selective scan   per channel c and state n, token by token:
-//                      dt = softplus(dtz[c] + dt_bias[c]) (made once per token and channel by a kernel ahead of the scan);  S[c][n] = exp(dt * A[c][n]) * S[c][n] + dt * x[c] * B[n];
+//                      dt = softplus(dtz[c] + dt_bias[c]) (made once per token and channel by a kernel ahead of the scan);
+//                      S[c][n] = exp(dt * A[c][n]) * S[c][n] + dt * x[c] * B[n];
 //                      y[c] = sum_n S[c][n] * C[n] + D[c] * x[c];  out[c] = y[c] * silu(z[c])
 //   duality form     per head h (group g = h / (heads / groups)) with S [N][V], token by token:
-//                      dt = softplus(dtr[h] + dt_bias[h]);  S = exp(-A[h] * dt) * S + dt * B[g] x[h]^T;
-//                      y[h] = S^T C[g] + D[h] * x[h]
+//                      dt = softplus(dtr[h] + dt_bias[h]) and exp(-A[h] * dt) (made once per token and head, likewise);
+//                      S = exp(-A[h] * dt) * S + dt * B[g] x[h]^T;  y[h] = S^T C[g] + D[h] * x[h]
 //   gate and norm    v = y * silu(z); every one of `groups` equal parts of the row divided by its own root mean
 //                    square (eps inside the root), times the weight, times a constant
 //
@@ -224,7 +225,10 @@ ssd_scan_kernel(const float* __restrict__ xbc, long ld, int x_off, int b_off, in
         for (int i = 0; i < CH; i += 4) {
             float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (!zero && n0 + i < N) v4 = *reinterpret_cast<const float4*>(init + i);
-            S[i] = v4.x; S[i + 1 < CH ? i + 1 : i] = v4.y; S[i + 2 < CH ? i + 2 : i] = v4.z; S[i + 3 < CH ? i + 3 : i] = v4.w;
+            S[i] = v4.x;
+            if (i + 1 < CH) S[i + 1] = v4.y;
+            if (i + 2 < CH) S[i + 2] = v4.z;
+            if (i + 3 < CH) S[i + 3] = v4.w;
         }
     } else {
 #pragma unroll

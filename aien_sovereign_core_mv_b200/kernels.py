@@ -186,7 +186,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "aien_grouped_gated_rmsnorm": [P, L, P, I, L, P, I, F, P, I, L, I, I, I, I, P],
         "aien_paged_attention_decode_fused": [P, L, P, L, P, L, P, P, I, F, P, P, I, P, P, P, P, I, P, P, L, P, P, P,
                                               I, I, I, I, I, F, I, I, P],
-        "aien_conv_act": [P, L, I, I, P, I, P, I, I, I, P, c_size_t, P, P, P, P, P, L, I, P],
+        "aien_conv_act": [P, L, I, I, P, I, P, I, I, I, P, c_size_t, P, P, P, P, P, L, P, L, I, P],
         "aien_selective_scan": [P, L, P, L, P, L, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, I, L, I, I, I, I, I, I, P, P],
         "aien_ssd_scan": [P, L, I, I, I, P, L, P, P, P, I, P, c_size_t, c_size_t, P, P, P, P, L, I, I, I, I, I, I, I, I, P, P, P],
         "aien_gate_group_norm": [P, L, P, L, P, I, F, F, P, I, L, I, I, I, P],
@@ -1709,19 +1709,22 @@ def biased_attention(ctx, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
 # ---------------------------------------------------------------------------- state-space recurrences
 def conv_act(proj: torch.Tensor, off: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor], taps: int, act: str,
              state: Optional[torch.Tensor], slot_map: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
-             positions: torch.Tensor, out: torch.Tensor) -> None:
+             positions: torch.Tensor, out: torch.Tensor, out16: Optional[torch.Tensor] = None) -> None:
     """out[t, c] = f(sum_j w[c, j] * u[t - taps + 1 + j, c] + bias[c]) for the ``channels`` columns of the float32 rows
     ``proj`` [T, *] from column ``off`` on; f the identity ("none") or silu.  Rows before a portion come from the
     request's state row (its first (taps - 1) * channels numbers, the newest row last; zeros at a sequence's start),
-    which is rewritten with the portion's last rows.  out float32 [T, >= channels]."""
-    _dev(proj, w, bias, state, slot_map, seq_of_token, q_start, positions, out)
+    which is rewritten with the portion's last rows.  out float32 [T, >= channels]; ``out16`` (bfloat16 [T, >= channels]): the
+    same rows once more, rounded, for a product that follows."""
+    _dev(proj, w, bias, state, slot_map, seq_of_token, q_start, positions, out, out16)
+    assert out16 is None or (out16.dtype == torch.bfloat16 and out16.stride(1) == 1 and out16.shape[0] == proj.shape[0])
     T = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1
     assert w.is_contiguous() and tuple(w.shape) == (channels, taps) and (bias is None or (bias.is_contiguous() and bias.numel() == channels))
     assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.stride(-1) == 1 and state.shape[-1] >= (taps - 1) * channels)
     _check(lib().aien_conv_act(_p(proj), proj.stride(0), int(off), int(channels), _p(w), dt(w), _p(bias), dt(bias) if bias is not None else F32,
                                int(taps), {"none": 0, "silu": 1}[act], _p(state), state.stride(0) if state is not None else 0, _p(slot_map),
-                               _p(seq_of_token), _p(q_start), _p(positions), _p(out), out.stride(0), T, _stream()), "conv_act")
+                               _p(seq_of_token), _p(q_start), _p(positions), _p(out), out.stride(0), _p(out16),
+                               out16.stride(0) if out16 is not None else 0, T, _stream()), "conv_act")
 
 
 SCAN_SEGMENT_MIN_TOKENS = 128        # steps with fewer tokens walk every portion in one piece

@@ -115,12 +115,10 @@ class SelectiveScan(Mixer):
         state = group.storage["state"][run.slot]
         proj = linear(ctx, h, self.w_in, out_dtype=torch.float32)                       # x | z
         x = ws.take((T, I), torch.float32)
+        # the x_proj product's operand in the compute dtype leaves the convolution's kernel beside the float32 rows
+        xa = ws.take((T, I), ctx.dtype) if ctx.dtype != torch.float32 else x
         K.conv_act(proj, 0, I, self.conv, self.conv_b, self.taps, "silu", state, group.slot_map, ctx.seq_of_token, ctx.q_start,
-                   ctx.positions, x)
-        xa = x
-        if ctx.dtype != torch.float32:                                                  # the product's operand in the compute dtype
-            xa = ws.take((T, I), ctx.dtype)
-            K.convert(x, xa)
+                   ctx.positions, x, xa if xa is not x else None)
         xp = linear(ctx, xa, self.w_x, out_dtype=torch.float32)                         # dt | B | C
         dtz = linear(ctx, xp[:, :R], self.w_dt, out_dtype=torch.float32)                # float32 step sizes into the softplus
         y = ws.take((T, I), ctx.dtype)

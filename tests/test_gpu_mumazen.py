@@ -440,7 +440,7 @@ def test_capped_attention_sees_far_keys_as_the_cap_allows(dtype, cap, page, head
     run([(0, 0, 300), (1, 0, 45)])                                 # whole prompts: the first tokens, every page border
     run([(0, 140, 130), (1, 44, 1)])                               # a portion over the big key in the middle beside a single token
     run([(0, 299, 1), (1, 22, 1)])                                 # single tokens (decoding), far from position 0
-    run([(1, 21, 2), (0, 127, 3), (0, 0, 0)][:2])                  # two tokens before the big key, three across a page border
+    run([(1, 21, 2), (0, 127, 3)])                                 # two tokens before the big key, three across a page border
 
 
 @pytest.mark.parametrize("E,identity,top,shared_gate", [(5, 2, 2, True), (4, 0, 1, False), (6, 3, 9, True), (3, 1, 2, False), (40, 8, 6, True)])
@@ -627,8 +627,6 @@ def test_long_decoding_bfloat16_graphs(models):
     steps = [([(4, a[:15], [14]), (3, b[:4], [3])], [])]
     for i in range(min(len(a) - 15, len(b) - 4)):
         steps.append(([(4, [a[15 + i]], [0]), (3, [b[4 + i]], [0])], []))
-    for i in range(4 + len(steps) - 1, len(b)):
-        pass
     check(H.run_steps(eng, steps), want, BF16_TOL, "A bfloat16 long decoding")
     assert len(eng._graphs) > 0                                     # the decode-only steps ran as captured graphs
 
